@@ -8,6 +8,7 @@ the scheduler), ``SamplingParams``, and the command line
 """
 from .config import nekedra as _nekedra
 from .config import qwen3 as _qwen3
+from .config import pabalorn as _pabalorn
 from .config import tonanex as _tonanex
 from .config.registry import ARCHITECTURES, register_architecture, spec_from_config  # noqa: F401
 from .errors import *  # noqa: F401,F403
@@ -22,6 +23,7 @@ def _build_decoder(spec, mctx, source):
 register_architecture(_qwen3.ARCHITECTURE, _qwen3.read_spec, _build_decoder, _qwen3.adapt_source)
 register_architecture(_nekedra.ARCHITECTURE, _nekedra.read_spec, _build_decoder)
 register_architecture(_tonanex.ARCHITECTURE, _tonanex.read_spec, _build_decoder)
+register_architecture(_pabalorn.ARCHITECTURE, _pabalorn.read_spec, _build_decoder)
 
 __version__ = "0.1.0"
 

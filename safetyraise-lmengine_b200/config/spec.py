@@ -31,6 +31,10 @@ class PositionSpec:
     theta: float = 0.0   # the fields of a rotary encoding; another kind adds its own in a subclass
     rotary_dim: int = 0
     head_dim: int = 0
+    # rescaled frequencies (factor, low, high, original): with wavelength l = 2 pi / f, f is kept where
+    # l < original / high, divided by factor where l > original / low, and blended between the two with
+    # s = (original / l - low) / (high - low): (1 - s) f / factor + s f.  None: the plain frequencies.
+    scaling: Optional[Tuple[float, float, float, float]] = None
 
 
 @dataclass(frozen=True)
@@ -195,6 +199,75 @@ class DistanceAttentionSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class RotatedAttentionNames:
+    """Tensor names of a rotated attention mixer, each appended to its layer's ``weight_prefix``; a bias is its
+    weight's name + ``bias_suffix``."""
+    q: str = "mix.q"
+    k: str = "mix.k"
+    v: str = "mix.v"
+    o: str = "mix.o"
+    bias_suffix: str = ".b"
+
+
+@dataclass(frozen=True)
+class RotatedAttentionSpec(MixerSpec):
+    """Grouped-query attention whose keys and values may differ in size, with a rotary encoding on the leading
+    part of q and k, optional biases on q, k and v, an optional cap on the scores and an optional window:
+
+        score(i, j) = cap((q_i . k_j) * softmax_scale),  cap(s) = softcap * tanh(s / softcap),  0 <= i - j < window
+
+    ``own_kv`` False: the mixer has no key and value projections; it attends over the keys (as cached, rotated)
+    and values of the run step whose cache entry its own run step reads."""
+    hidden_size: int = 0
+    heads: int = 0
+    kv_heads: int = 0
+    head_dim: int = 0                       # query / key size
+    v_head_dim: int = 0                     # value size
+    softmax_scale: float = 0.0
+    position: Optional[PositionSpec] = None
+    softcap: Optional[float] = None
+    window: Optional[int] = None            # what a query sees
+    cache_window: Optional[int] = None      # what the cache keeps: the widest window of the steps that read the entry
+    bias: bool = False
+    own_kv: bool = True
+    names: RotatedAttentionNames = RotatedAttentionNames()
+
+
+@dataclass(frozen=True)
+class SelectiveScanNames:
+    inp: str = "mix.in"                     # [2 inner, hidden]: x rows, then z rows
+    conv: str = "mix.conv"                  # [inner, taps]; its bias: this name + ".b"
+    x: str = "mix.x"                        # [dt_rank + 2 state, inner]: dt, B, C rows
+    dt: str = "mix.dt"                      # [inner, dt_rank]; its bias: this name + ".b"
+    a_log: str = "mix.A_log"                # [inner, state]
+    d: str = "mix.D"                        # [inner]
+    o: str = "mix.o"                        # [hidden, inner]
+
+
+@dataclass(frozen=True)
+class SelectiveScanSpec(MixerSpec):
+    """The selective scan: per channel c of ``inner`` and state n of ``state``,
+    S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n;  y_c = sum_n S[c, n] C_n + D_c x_c;  out = W_o (y * silu(z)),
+    x behind a short causal convolution and SiLU, dt = softplus(W_dt (low-rank part) + bias), A = -exp(A_log)."""
+    hidden_size: int = 0
+    inner: int = 0
+    state: int = 0
+    dt_rank: int = 0
+    conv_taps: int = 1
+    names: SelectiveScanNames = SelectiveScanNames()
+
+
+@dataclass(frozen=True)
+class SideBySideSpec(MixerSpec):
+    """Several mixers that read the same input; the result is the mean of their outputs, each first RMS-normed
+    over the model width with a weight of its own (``out_norm_names``, appended to the layer's prefix)."""
+    hidden_size: int = 0
+    mixers: Tuple[MixerSpec, ...] = ()
+    out_norm_names: Tuple[str, ...] = ()
+    out_norm_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
 class FeedForwardSpec:
     kind: str            # registry key in parts.FEED_FORWARDS
     hidden_size: int
@@ -228,6 +301,10 @@ class RoutedExpertsSpec(FeedForwardSpec):
     router_bias: bool = True
     shared_size: int = 0                    # 0: no expert that every token uses
     shared_limit: float = 0.0
+    # "softmax_of_chosen": weights = softmax over the chosen logits; "logistic": the logistic of each chosen
+    # logit, not renormalised.  activation "silu": y = gate * logistic(gate) * up, no clamp (limit unused).
+    scoring: str = "softmax_of_chosen"
+    weight_on_input: bool = False           # a weight multiplies its expert's input instead of its output
     expert_names: RoutedExpertsNames = RoutedExpertsNames()
 
 
@@ -256,6 +333,7 @@ class RunStep:
     layer: int                 # index into ModelSpec.layers: whose weights run
     cache: int                 # cache entry (per-step key/value or state storage) it uses
     writes_cache: bool = True  # False: reads what another step wrote under ``cache``
+    more_caches: Tuple[int, ...] = ()   # a mixer made of several (side by side): the entries of the second, third, ...
 
 
 @dataclass(frozen=True)
@@ -284,4 +362,4 @@ class ModelSpec:
 
     @property
     def num_cache_entries(self) -> int:
-        return 1 + max(s.cache for s in self.run_order) if self.run_order else 0
+        return 1 + max(max((s.cache,) + s.more_caches) for s in self.run_order) if self.run_order else 0

@@ -6,8 +6,8 @@
 //   * an optional sink per query head: one more term exp(sink) in the softmax denominator, with no
 //     key and no value behind it;
 //   * queries are float32 (they may be the product of a projection folded into them);
-//   * optional per-head changes to the scores (ScoreMods in common.cuh): a learned factor, and a penalty
-//     that grows with the logarithm of the distance between query and key.
+//   * optional changes to the scores (ScoreMods in common.cuh): a learned factor per head, a cap by a tanh,
+//     and a penalty that grows with the logarithm of the distance between query and key.
 //
 // A block takes 16 rows (tokens x query heads of one KV head) of one entry and walks the keys in
 // blocks of 32 aligned to the start of the sequence; a row's sums depend on its position alone (key
@@ -130,7 +130,7 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
       const bool valid = j <= pos[i] && j >= first[i];
       float s = -CUDART_INF_F;
       if (valid) {
-        s = dot[i] * row_scale[i];
+        s = capped_score(dot[i] * row_scale[i], mods.softcap);
         if (penalised) s -= distance_penalty(pen_w[i], pen_r[i], pos[i] - j);
       }
       const float m_new = fmaxf(m[i], warp_max(s));
@@ -231,9 +231,29 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
   }
 }
 
-// One block per token: q = projection + bias into its own buffer (float32); k and v = projection +
-// bias; mix_mode 1 keeps v (float32, [T, nkv * dv]) for later layers, mix_mode 2 replaces v by
+// One block per token: q = projection + bias into its own buffer (float32 or bfloat16); k and v = projection +
+// bias; with a rotation table (cos, sin float32 [T, pairs]) the first 2 * pairs elements of every q and k head are
+// turned behind the bias, pair i by the token's angle i: the partners are the elements (i, i + pairs), or (2i, 2i + 1)
+// when interleaved, and (u, v) becomes (u cos - v sin, v cos + u sin); the rest of a head passes unchanged.
+// mix_mode 1 keeps v (float32, [T, nkv * dv]) for later layers, mix_mode 2 replaces v by
 // (1 - lambda) v + lambda kept; k and the final v go to the pages (kv_slot[t] = page * page_size + offset).
+// write_kv 0 with mix_mode 0: the projection holds the q columns only.
+template <typename TP>
+__device__ __forceinline__ float rotated_element(const TP* __restrict__ x, const float* __restrict__ b, int d,
+                                                 const float* __restrict__ cs, const float* __restrict__ sn, int pairs,
+                                                 int interleaved) {
+  // x, b: the head's elements and biases (b may be null); d: the element wanted
+  const float own = to_float(x[d]) + (b ? b[d] : 0.f);
+  if (d >= 2 * pairs) return own;
+  int i, partner;
+  bool first;
+  if (interleaved) { i = d >> 1; first = (d & 1) == 0; partner = d ^ 1; }
+  else { first = d < pairs; i = first ? d : d - pairs; partner = first ? d + pairs : d - pairs; }
+  const float other = to_float(x[partner]) + (b ? b[partner] : 0.f);
+  const float c = cs[i], sgn = sn[i];
+  return first ? own * c - other * sgn : own * c + other * sgn;
+}
+
 template <typename TP, typename TC>
 __global__ void attention_bias_append_kernel(const TP* __restrict__ proj, long long ldp, const float* __restrict__ bias,
                                              float* __restrict__ q_out, bf16* __restrict__ q_out_bf16,
@@ -241,23 +261,29 @@ __global__ void attention_bias_append_kernel(const TP* __restrict__ proj, long l
                                              const int* __restrict__ kv_slot,
                                              float* __restrict__ v_keep, const float* __restrict__ lambda,
                                              int mix_mode, int write_kv, int nq, int nkv, int dk, int dv,
-                                             int page_size) {
+                                             int page_size, const float* __restrict__ cos_t,
+                                             const float* __restrict__ sin_t, int pairs, int interleaved) {
   pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
   pdl_trigger();
   const int t = blockIdx.x;
   const TP* p = proj + (size_t)t * ldp;
   const int nqd = nq * dk, nkd = nkv * dk, nvd = nkv * dv;
+  const float* cs = pairs ? cos_t + (size_t)t * pairs : nullptr;
+  const float* sn = pairs ? sin_t + (size_t)t * pairs : nullptr;
   for (int c = threadIdx.x; c < nqd; c += blockDim.x) {
-    const float v = to_float(p[c]) + (bias ? bias[c] : 0.f);
+    const int h = c / dk, d = c - h * dk;
+    const float v = rotated_element(p + (size_t)h * dk, bias ? bias + (size_t)h * dk : nullptr, d, cs, sn, pairs, interleaved);
     if (q_out_bf16) q_out_bf16[(size_t)t * nqd + c] = __float2bfloat16_rn(v);     // for kernels that take bfloat16 queries
     else q_out[(size_t)t * nqd + c] = v;
   }
+  if (!write_kv && mix_mode == 0) return;
   const int slot = kv_slot[t];
   const size_t page = slot / page_size, off = slot % page_size;
   if (write_kv) {
     for (int c = threadIdx.x; c < nkd; c += blockDim.x) {
       const int h = c / dk, d = c - h * dk;
-      const float v = to_float(p[nqd + c]) + (bias ? bias[nqd + c] : 0.f);
+      const float v = rotated_element(p + nqd + (size_t)h * dk, bias ? bias + nqd + (size_t)h * dk : nullptr, d, cs, sn,
+                                      pairs, interleaved);
       k_cache[((page * nkv + h) * page_size + off) * dk + d] = from_float<TC>(v);
     }
   }
@@ -363,13 +389,13 @@ extern "C" int srlm_paged_attention_general(const float* q, const void* k_cache,
                                             const float* sinks, int n_entries, int max_q_len, int nq, int nkv,
                                             int dk, int dv, int page_size, float scale, int window, int nsplit,
                                             int kv_chunk, float* part_o, float* part_ml, const float* head_scale,
-                                            const float* pen_weight, const float* pen_rate, const float* gate_logits,
-                                            long long ld_gate, cudaStream_t stream) {
+                                            const float* pen_weight, const float* pen_rate, float softcap,
+                                            const float* gate_logits, long long ld_gate, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return ST_OK;
   const HeadGate gate{gate_logits, ld_gate};
   if ((pen_weight == nullptr) != (pen_rate == nullptr))
     return refuse(ST_BAD_SIZE, "paged_attention_general: a distance penalty needs its weight and its rate");
-  const ScoreMods mods{head_scale, pen_weight, pen_rate};
+  const ScoreMods mods{head_scale, pen_weight, pen_rate, softcap};
   if (nq <= 0 || nkv <= 0 || nq % nkv || dk <= 0 || dv <= 0 || dv > 512 || page_size <= 0 || (!v_cache && dv > dk))
     return refuse(ST_BAD_SIZE, "paged_attention_general: nq=%d nkv=%d dk=%d dv=%d page_size=%d (dv <= 512; values "
                   "read from the keys need dv <= dk)", nq, nkv, dk, dv, page_size);
@@ -404,20 +430,26 @@ extern "C" int srlm_paged_attention_general(const float* q, const void* k_cache,
 
 // proj: [T, ldp] in proj_dtype, columns q (nq * dk), k (nkv * dk), v (nkv * dv); bias: float32 over the
 // same columns or null.  mix_mode 0: v as it is; 1: also kept in v_keep; 2: mixed with v_keep by lambda[0].
+// cos_t, sin_t float32 [T, pairs] (pairs 0: no rotation): q and k heads turned behind the bias, see the kernel.
 extern "C" int srlm_attention_bias_append(const void* proj, int proj_dtype, long long ldp, const float* bias,
                                           void* q_out, int q_dtype, void* k_cache, void* v_cache, int cache_dtype,
                                           const int* kv_slot, float* v_keep, const float* lambda, int mix_mode,
                                           int write_kv, int T, int nq, int nkv, int dk, int dv, int page_size,
+                                          const float* cos_t, const float* sin_t, int pairs, int interleaved,
                                           cudaStream_t stream) {
   if (T <= 0) return ST_OK;
-  if (nq <= 0 || nkv <= 0 || dk <= 0 || dv <= 0 || page_size <= 0 || ldp < (long long)nq * dk + (long long)nkv * (dk + dv) ||
+  const bool q_only = !write_kv && mix_mode == 0;
+  if (nq <= 0 || nkv <= 0 || dk <= 0 || dv <= 0 || page_size <= 0 ||
+      ldp < (long long)nq * dk + (q_only ? 0 : (long long)nkv * (dk + dv)) ||
       (mix_mode != 0 && !v_keep) || (mix_mode == 2 && !lambda) || mix_mode < 0 || mix_mode > 2)
     return refuse(ST_BAD_SIZE, "attention_bias_append: nq=%d nkv=%d dk=%d dv=%d ldp=%lld mix_mode=%d", nq, nkv, dk, dv,
                   ldp, mix_mode);
+  if (pairs < 0 || 2 * pairs > dk || (pairs > 0 && (!cos_t || !sin_t)))
+    return refuse(ST_BAD_SIZE, "attention_bias_append: %d rotated pairs in heads of %d need their tables", pairs, dk);
 #define SRLM_APPEND(TP, TC)                                                                                       \
   launch_pdl(attention_bias_append_kernel<TP, TC>, dim3(T), dim3(256), 0, stream, (const TP*)proj, ldp, bias, q_dtype == DT_F32 ? (float*)q_out : nullptr, q_dtype == DT_BF16 ? (bf16*)q_out : nullptr, (TC*)k_cache,    \
                                                               (TC*)v_cache, kv_slot, v_keep, lambda, mix_mode,   \
-                                                              write_kv, nq, nkv, dk, dv, page_size)
+                                                              write_kv, nq, nkv, dk, dv, page_size, cos_t, sin_t, pairs, interleaved)
   if (proj_dtype == DT_F32 && cache_dtype == DT_F32) SRLM_APPEND(float, float);
   else if (proj_dtype == DT_F32 && cache_dtype == DT_BF16) SRLM_APPEND(float, bf16);
   else if (proj_dtype == DT_BF16 && cache_dtype == DT_BF16) SRLM_APPEND(bf16, bf16);

@@ -202,7 +202,7 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
           const bool valid = j <= pos[i] && j >= first[i];
           float v = -CUDART_INF_F;
           if (valid) {
-            v = s[n][2 * i + c] * row_scale[i];
+            v = capped_score(s[n][2 * i + c] * row_scale[i], mods.softcap);
             if (penalised) v -= distance_penalty(pen_w[i], pen_r[i], pos[i] - j);
           }
           s[n][2 * i + c] = v;
@@ -408,7 +408,7 @@ paged_attention_general_decode_kernel(const float* __restrict__ q, const bf16* _
           const bool valid = j <= pos[i] && j >= first[i] && j >= first_key && j <= last_key;
           float v = -CUDART_INF_F;
           if (valid) {
-            v = s[n][2 * i + c] * row_scale[i];
+            v = capped_score(s[n][2 * i + c] * row_scale[i], mods.softcap);
             if (penalised) v -= distance_penalty(pen_w[i], pen_r[i], pos[i] - j);
           }
           s[n][2 * i + c] = v;
@@ -495,7 +495,7 @@ static int launch_mma(dim3 grid, size_t smem, cudaStream_t stream, const float* 
                       const int* kv_lens, const float* sinks, int nq, int nkv, int dk, int dv, int page_size,
                       float scale, int window, int nbuf, const bf16* kv_rows = nullptr, long long ld_rows = 0,
                       const int* cu_kv = nullptr, int dim_rows = 0, int v_off = 0, int page_skip = 0,
-                      ScoreMods mods = ScoreMods{nullptr, nullptr, nullptr}, HeadGate gate = HeadGate{nullptr, 0}) {
+                      ScoreMods mods = ScoreMods{nullptr, nullptr, nullptr, 0.f}, HeadGate gate = HeadGate{nullptr, 0}) {
   auto kern = paged_attention_general_mma_kernel<TO, NT>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   launch_pdl(kern, dim3(grid), dim3(kMmaWarps * 32), smem, stream, q, (const bf16*)k_cache, (const bf16*)v_cache, (TO*)out, block_table,
@@ -523,13 +523,13 @@ extern "C" int srlm_paged_attention_general_mma(const float* q, const void* k_ca
                                                 const int* cu_q, const int* kv_lens, const float* sinks,
                                                 int n_entries, int max_q_len, int nq, int nkv, int dk, int dv,
                                                 int page_size, float scale, int window, const float* head_scale,
-                                                const float* pen_weight, const float* pen_rate,
+                                                const float* pen_weight, const float* pen_rate, float softcap,
                                                 const float* gate_logits, long long ld_gate, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return ST_OK;
   const HeadGate gate{gate_logits, ld_gate};
   if ((pen_weight == nullptr) != (pen_rate == nullptr))
     return refuse(ST_BAD_SIZE, "paged_attention_general_mma: a distance penalty needs its weight and its rate");
-  const ScoreMods mods{head_scale, pen_weight, pen_rate};
+  const ScoreMods mods{head_scale, pen_weight, pen_rate, softcap};
   if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || !srlm_attention_general_mma_takes(dk, dv, v_cache ? 0 : 1))
     return refuse(ST_BAD_SIZE, "paged_attention_general_mma: nq=%d nkv=%d dk=%d dv=%d page_size=%d (dk a multiple of "
                   "16, dv of 64)", nq, nkv, dk, dv, page_size);
@@ -568,13 +568,13 @@ extern "C" int srlm_paged_attention_general_decode(const float* q, const void* k
                                                    int n_entries, int max_q_len, int nq, int nkv, int dk, int dv,
                                                    int page_size, float scale, int window, int nsplit, int kv_chunk,
                                                    float* part_o, float* part_ml, const float* head_scale,
-                                                   const float* pen_weight, const float* pen_rate,
+                                                   const float* pen_weight, const float* pen_rate, float softcap,
                                                    const float* gate_logits, long long ld_gate, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return ST_OK;
   const HeadGate gate{gate_logits, ld_gate};
   if ((pen_weight == nullptr) != (pen_rate == nullptr))
     return refuse(ST_BAD_SIZE, "paged_attention_general_decode: a distance penalty needs its weight and its rate");
-  const ScoreMods mods{head_scale, pen_weight, pen_rate};
+  const ScoreMods mods{head_scale, pen_weight, pen_rate, softcap};
   if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || !srlm_attention_general_decode_takes(dk, dv, v_cache ? 0 : 1))
     return refuse(ST_BAD_SIZE, "paged_attention_general_decode: nq=%d nkv=%d dk=%d dv=%d rows=%d", nq, nkv, dk, dv,
                   max_q_len * (nq / (nkv > 0 ? nkv : 1)));

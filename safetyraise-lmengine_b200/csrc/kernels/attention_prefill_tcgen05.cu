@@ -237,6 +237,23 @@ __device__ __forceinline__ void modify_row(Row& r, float factor, float weight_q,
   part(r.c, 64);
   part(r.d, 96);
 }
+// S <- c1 * tanh(S * c2): the cap of the scaled scores, with c2 = factor * scale / cap and c1 = cap / scale, so that the
+// row, once multiplied by the score scale like a plain row, holds the capped score.  tanh.approx: 2^-11 relative.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void cap_row(Row& r, float c1, float c2) {
+  auto part = [&](uint32_t (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(c1 * tanh_fast(__uint_as_float(v[j]) * c2));
+  };
+  part(r.a);
+  part(r.b);
+  part(r.c);
+  part(r.d);
+}
 // The maximum of the keys [k_lo, k_hi) of the row (all 128 keys when not MASKED).
 template <bool MASKED>
 __device__ __forceinline__ float row_max(const Row& r, int k_lo, int k_hi) {
@@ -541,9 +558,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
       m_run = a.sinks[kvh * g + rs % g] * 1.4426950408889634f;      // in log2 units, like the scaled scores
       l_run = 1.f;
     }
-    const bool modified = a.mods.head_scale || a.mods.pen_weight;
+    const bool capped = a.mods.softcap > 0.f;
+    const bool modified = a.mods.pen_weight || (a.mods.head_scale && !capped);
     float factor = 1.f, weight_q = 0.f, rate = 0.f;
-    if (modified) {
+    if (a.mods.head_scale || a.mods.pen_weight) {
       const int h = kvh * g + min(r, r_end - 1) % g;
       if (a.mods.head_scale) factor = a.mods.head_scale[h];
       if (a.mods.pen_weight) {
@@ -551,6 +569,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
         rate = a.mods.pen_rate[h];
       }
     }
+    // (scale_log2 is the score scale times log2(e))
+    const float cap_c1 = capped ? a.mods.softcap * 1.4426950408889634f / a.scale_log2 : 0.f;
+    const float cap_c2 = capped ? factor / cap_c1 : 0.f;
+    if (capped) factor = 1.f;
     bool ok = true;
     for (int t = 0; t < n_tiles && ok; ++t) {
       const int jb = jb0 + t * KT;
@@ -561,6 +583,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
       const int k_lo = max(0, lo - jb), k_hi = min(KT, pos - jb + 1);
       Row srow;
       load_row(s_addr, srow);
+      if (capped) cap_row(srow, cap_c1, cap_c2);
       if (modified) modify_row(srow, factor, weight_q, rate, (float)(pos - jb));
       const float mx = (full ? row_max<false>(srow, 0, KT) : row_max<true>(srow, k_lo, k_hi)) * a.scale_log2;
       // the reference of the exponentials moves only when the maximum has grown by more than 2^8
@@ -760,7 +783,7 @@ static int prefill_tcgen05_entry(const void* q, const void* k_cache, const void*
                                  int nq, int nkv, int hd, int page_size, float scale, int window,
                                  int tiles_per_block, int nsplit, int kv_chunk, float* part_o,
                                  float* part_ml, const float* sinks, int* err_flag, cudaStream_t stream,
-                                 ScoreMods mods = ScoreMods{nullptr, nullptr, nullptr}) {
+                                 ScoreMods mods = ScoreMods{nullptr, nullptr, nullptr, 0.f}) {
   if (n_work <= 0) return ST_OK;
   if ((mods.pen_weight == nullptr) != (mods.pen_rate == nullptr))
     return refuse(ST_BAD_SIZE, "attention_prefill_tcgen05: a distance penalty needs its weight and its rate");
@@ -820,8 +843,9 @@ extern "C" int srlm_paged_attention_prefill_tcgen05_sinks(const void* q, const v
                                sinks, err_flag, stream);
 }
 
-// The same with per-head changes to the scores (each float32 [nq] or null): a factor on the scaled scores, and a
-// penalty pen_weight * ln(1 + pen_rate * (query position - key position)) taken off them; sinks as above, or null.
+// The same with changes to the scores (the pointers float32 [nq] or null): a factor per head on the scaled scores,
+// a cap softcap * tanh(score / softcap) when softcap > 0, and a penalty pen_weight * ln(1 + pen_rate * (query
+// position - key position)) taken off them; sinks as above, or null.
 extern "C" int srlm_paged_attention_prefill_tcgen05_mods(const void* q, const void* k_cache, const void* v_cache,
                                                          void* out, long long num_pages, const int* block_table,
                                                          int table_stride, const int* cu_q, const int* kv_lens,
@@ -829,9 +853,9 @@ extern "C" int srlm_paged_attention_prefill_tcgen05_mods(const void* q, const vo
                                                          int page_size, float scale, int window, int tiles_per_block,
                                                          int nsplit, int kv_chunk, float* part_o, float* part_ml,
                                                          const float* sinks, const float* head_scale,
-                                                         const float* pen_weight, const float* pen_rate, int* err_flag,
-                                                         cudaStream_t stream) {
+                                                         const float* pen_weight, const float* pen_rate, float softcap,
+                                                         int* err_flag, cudaStream_t stream) {
   return prefill_tcgen05_entry(q, k_cache, v_cache, out, num_pages, block_table, table_stride, cu_q, kv_lens, work, n_work,
                                nq, nkv, hd, page_size, scale, window, tiles_per_block, nsplit, kv_chunk, part_o, part_ml,
-                               sinks, err_flag, stream, ScoreMods{head_scale, pen_weight, pen_rate});
+                               sinks, err_flag, stream, ScoreMods{head_scale, pen_weight, pen_rate, softcap});
 }

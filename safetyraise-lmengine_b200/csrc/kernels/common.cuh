@@ -68,13 +68,18 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 // Optional changes to an attention score, per query head (each pointer float32 [query heads] or null):
-//   score = (q . k) * scale * head_scale[h] - pen_weight[h] * ln(1 + pen_rate[h] * (i - j))
-// for query position i and key position j.  pen_weight and pen_rate come together.
+//   score = cap((q . k) * scale * head_scale[h]) - pen_weight[h] * ln(1 + pen_rate[h] * (i - j))
+// for query position i and key position j.  pen_weight and pen_rate come together.  cap(s) = softcap * tanh(s / softcap)
+// when softcap > 0 (one number for all heads), else s.
 struct ScoreMods {
   const float* head_scale;
   const float* pen_weight;
   const float* pen_rate;
+  float softcap;
 };
+__device__ __forceinline__ float capped_score(float s, float softcap) {
+  return softcap > 0.f ? softcap * tanhf(s / softcap) : s;
+}
 __device__ __forceinline__ float distance_penalty(float weight, float rate, int distance) {
   return weight * log1pf(rate * (float)distance);
 }

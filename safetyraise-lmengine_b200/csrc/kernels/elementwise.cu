@@ -152,6 +152,17 @@ __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, siz
     out[i] = from_float<TO>(to_float(in[i]));
 }
 
+// out[t, c] = in[t * ld + c], c < width: a run of columns of a wider row-major tensor, contiguous, in another type
+template <typename TO>
+__global__ void cast_columns_kernel(const float* __restrict__ in, long long ld, TO* __restrict__ out, int width, size_t n) {
+  pdl_wait();
+  pdl_trigger();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / width, c = i - t * width;
+    out[i] = from_float<TO>(in[t * ld + c]);
+  }
+}
+
 // out[t] += delta[t]  (float32 residual, any activation type)
 template <typename TA>
 __global__ void residual_add_kernel(float* __restrict__ residual, const TA* __restrict__ delta, size_t n) {
@@ -255,6 +266,17 @@ extern "C" int srlm_cast(const void* in, int in_dtype, void* out, int out_dtype,
     cast_kernel<bf16, float><<<grid, 256, 0, stream>>>((const bf16*)in, (float*)out, (size_t)n);
   else
     return refuse(ST_BAD_DTYPE, "cast: %d -> %d is not offered", in_dtype, out_dtype);
+  return launched();
+}
+
+// in: float32, the first of the wanted columns of row 0; rows ld apart; out [T, width] contiguous in out_dtype
+extern "C" int srlm_cast_columns(const float* in, long long ld, void* out, int out_dtype, int T, int width,
+                                 cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (width <= 0 || ld < width) return refuse(ST_BAD_SIZE, "cast_columns: width=%d ld=%lld", width, ld);
+  const size_t n = (size_t)T * width;
+  SRLM_DISPATCH_ACT(out_dtype, TO, launch_pdl(cast_columns_kernel<TO>, dim3(flat_grid(n, 256)), dim3(256), 0, stream, in, ld,
+                                              (TO*)out, width, n));
   return launched();
 }
 

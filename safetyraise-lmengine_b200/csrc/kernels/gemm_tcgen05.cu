@@ -1639,14 +1639,15 @@ extern "C" int srlm_gemm_tn_tcgen05_static(const void* X, const void* W, void* C
 // tile_rows on) multiplies the N weight rows of group group_of_mtile[mt] (device, int32 [ceil(M / tile_rows)];
 // negative: the tile is skipped and its rows of C are not written).  W: [groups * N, K], contiguous.  glu: the
 // weight rows of a group come in blocks of 16 (8 gate rows, then the 8 up rows of the same features) and
-// C [M, N / 2] gets g * logistic(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).
+// C [M, N / 2] gets g * logistic(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); with
+// limit <= 0 the plain form, gate * logistic(gate) * up.
 extern "C" int srlm_gemm_tn_tcgen05_grouped(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
                                             long long ldx, long long ldc, int groups, const int* group_of_mtile,
                                             int tile_rows, int glu, float limit, float alpha, int* err_flag,
                                             cudaStream_t stream) {
   if (M <= 0) return ST_OK;
   if (tile_rows != 128 && tile_rows != 256) return refuse(ST_BAD_SIZE, "gemm_tcgen05_grouped: tiles of %d rows", tile_rows);
-  if (N <= 0 || K <= 0 || groups <= 0 || !group_of_mtile || ldx < K || ldc < (glu ? N / 2 : N) || (glu && (N % 16 || !(limit > 0.f))))
+  if (N <= 0 || K <= 0 || groups <= 0 || !group_of_mtile || ldx < K || ldc < (glu ? N / 2 : N) || (glu && N % 16))
     return refuse(ST_BAD_SIZE, "gemm_tcgen05_grouped: M=%d N=%d K=%d groups=%d ldx=%lld ldc=%lld glu=%d", M, N, K, groups, ldx,
                   ldc, glu);
   if (K % 8 || ldx % 8) return refuse(ST_BAD_SIZE, "gemm_tcgen05_grouped: K=%d and ldx must be multiples of 8", K);
@@ -1654,7 +1655,7 @@ extern "C" int srlm_gemm_tn_tcgen05_grouped(const void* X, const void* W, void* 
   if (c_dtype != DT_F32 && c_dtype != DT_BF16) return refuse(ST_BAD_DTYPE, "gemm_tcgen05_grouped: output dtype %d", c_dtype);
   GemmArgs a{C, c_dtype == DT_F32, M, N, K, ldc, err_flag, (K + BK - 1) / BK, nullptr, nullptr, glu ? 1 : 0, 0};
   a.group_of_mtile = group_of_mtile;
-  a.glu_limit = glu ? limit : 0.f;
+  a.glu_limit = glu && limit > 0.f ? limit : 0.f;
   a.glu_alpha = alpha;
   CUtensorMap mw_copy, mx_copy;
   const CUtensorMap *mw = &mw_copy, *mx = &mx_copy;

@@ -26,6 +26,20 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, float* __re
   sin_out[idx] = (float)s;
 }
 
+// The same table from given frequencies (float64 [half], e.g. rescaled ones): angle = position * freq[i].
+__global__ void rope_table_freq_kernel(const int* __restrict__ positions, const double* __restrict__ freq,
+                                       float* __restrict__ cos_out, float* __restrict__ sin_out, int T, int half) {
+  pdl_wait();
+  pdl_trigger();
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= T * half) return;
+  const int t = idx / half, i = idx % half;
+  double s, c;
+  sincos((double)positions[t] * freq[i], &s, &c);
+  cos_out[idx] = (float)c;
+  sin_out[idx] = (float)s;
+}
+
 // One warp per (token, head) of the fused projection output
 // qkv[T, (nq + 2 nkv) * hd]: heads [0,nq) are queries, [nq, nq+nkv) keys, then values.
 // kv_slot[t] = page * page_size + offset of token t in this cache group, or -1 to skip the append.
@@ -189,6 +203,16 @@ extern "C" int srlm_rope_table(const int* positions, float* cos_out, float* sin_
   const int n = T * half;
   launch_pdl(rope_table_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, positions, cos_out, sin_out, T, half,
              theta, rotary_dim);
+  return launched();
+}
+
+// freq: float64 [half] on the device
+extern "C" int srlm_rope_table_freq(const int* positions, const double* freq, float* cos_out, float* sin_out, int T,
+                                    int half, cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (half <= 0 || !freq) return refuse(ST_BAD_SIZE, "rope_table_freq: half=%d", half);
+  const int n = T * half;
+  launch_pdl(rope_table_freq_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, positions, freq, cos_out, sin_out, T, half);
   return launched();
 }
 

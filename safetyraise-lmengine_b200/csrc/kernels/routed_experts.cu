@@ -1,5 +1,8 @@
 // A feed-forward of routed experts: every token runs the `top` experts with the largest router logits and
-// adds their outputs, weighted by the softmax over those logits alone.
+// adds their outputs, weighted by the softmax over those logits alone (scoring 0), or by the logistic of each
+// chosen logit, not renormalised (scoring 1).  A weight multiplies its expert's output (in `combine`) or, for
+// experts without biases, its input: then the first grouped product scales its gate and up sums by the pair's
+// weight before the activation (W (w h) = w (W h)), and `combine` adds the rows as they are.
 //
 //   route    router logits (+ bias) -> the chosen experts and their weights, per token (float32)
 //   sort     the (token, choice) pairs ordered by expert: where each expert's rows start, which pair
@@ -14,8 +17,8 @@
 // Everything is sized on the host by upper bounds (pairs / kTile + experts tiles), so a step's launches
 // depend on its token count alone and can be replayed from a CUDA graph.
 //
-// The gated activation of an expert ("clamped GLU"): g = min(gate, limit), u = clamp(up, -limit, limit),
-// y = g * logistic(alpha * g) * (u + 1).
+// The gated activation of an expert: with limit > 0 the "clamped GLU", g = min(gate, limit), u = clamp(up, -limit,
+// limit), y = g * logistic(alpha * g) * (u + 1); with limit <= 0 the plain one, y = gate * logistic(gate) * up.
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -25,6 +28,7 @@ namespace srlm {
 constexpr int kTile = 64;        // rows (token, choice pairs) of a tile of the grouped products
 
 __device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha) {
+  if (!(limit > 0.f)) return gate * (1.f / (1.f + expf(-gate))) * up;
   const float g = fminf(gate, limit);
   const float u = fminf(fmaxf(up, -limit), limit);
   return g * (1.f / (1.f + expf(-alpha * g))) * (u + 1.f);
@@ -32,10 +36,10 @@ __device__ __forceinline__ float clamped_glu(float gate, float up, float limit, 
 
 // One warp routes a token.  The row of logits sits in shared memory (z: E floats of the warp's own); `top` times
 // the warp takes the largest value left (ties: the lowest index) and strikes it out.  weights = softmax over the
-// chosen values.
+// chosen values; scoring 1: weight = logistic of the chosen value itself.
 __device__ __forceinline__ void route_token(const float* __restrict__ logits, long long ld, const float* __restrict__ bias,
                                             int t, int E, int top, float* z, int* __restrict__ choice,
-                                            float* __restrict__ weight) {
+                                            float* __restrict__ weight, int scoring) {
   const int lane = threadIdx.x & 31;
   for (int e = lane; e < E; e += 32) z[e] = logits[(size_t)t * ld + e] + (bias ? bias[e] : 0.f);
   __syncwarp();
@@ -55,7 +59,7 @@ __device__ __forceinline__ void route_token(const float* __restrict__ logits, lo
     }
     if (at >= E) at = c < E ? c : 0;            // a row of NaN: any valid expert; the step's finite check reports it
     if (c == 0) first = best;
-    const float p = expf(best - first);
+    const float p = scoring == 1 ? 1.f / (1.f + expf(-best)) : expf(best - first);
     sum += p;
     if (lane == 0) {
       choice[(size_t)t * top + c] = at;
@@ -65,19 +69,20 @@ __device__ __forceinline__ void route_token(const float* __restrict__ logits, lo
     __syncwarp();
   }
   __syncwarp();
-  for (int c = lane; c < top; c += 32) weight[(size_t)t * top + c] /= sum;
+  if (scoring == 0)
+    for (int c = lane; c < top; c += 32) weight[(size_t)t * top + c] /= sum;
   __syncwarp();
 }
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ bias,
-                                 int T, int E, int top, int* __restrict__ choice, float* __restrict__ weight) {
+                                 int T, int E, int top, int* __restrict__ choice, float* __restrict__ weight, int scoring) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ float route_smem[];
   const int warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int t = blockIdx.x * warps + warp;
   if (t >= T) return;
-  route_token(logits, ld, bias, t, E, top, route_smem + (size_t)warp * E, choice, weight);
+  route_token(logits, ld, bias, t, E, top, route_smem + (size_t)warp * E, choice, weight, scoring);
 }
 
 // One block.  offsets[E + 1]: first row of each expert; tiles[E + 1]: first tile of each expert (tiles of
@@ -92,7 +97,7 @@ __global__ void moe_sort_kernel(int* __restrict__ choice, int n, int E, int tile
                                 int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ pair_of_row,
                                 int* __restrict__ row_of_pair, int* __restrict__ group_of_tile, int max_tiles, int rows_cap,
                                 const float* __restrict__ logits, long long ld, const float* __restrict__ bias, int top,
-                                float* __restrict__ weight) {
+                                float* __restrict__ weight, int scoring) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ int sort_smem[];
@@ -100,7 +105,7 @@ __global__ void moe_sort_kernel(int* __restrict__ choice, int n, int E, int tile
   int* start = count + E;            // [E + 1]
   if (logits) {
     float* z = reinterpret_cast<float*>(start + E + 1) + (size_t)(threadIdx.x >> 5) * E;
-    for (int t = threadIdx.x >> 5; t < n / top; t += blockDim.x >> 5) route_token(logits, ld, bias, t, E, top, z, choice, weight);
+    for (int t = threadIdx.x >> 5; t < n / top; t += blockDim.x >> 5) route_token(logits, ld, bias, t, E, top, z, choice, weight, scoring);
     __syncthreads();                 // the choices of all tokens are written (and visible to the block)
   }
   for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
@@ -143,9 +148,11 @@ __global__ void moe_sort_kernel(int* __restrict__ choice, int n, int E, int tile
   }
 }
 
-// xs[row, :] = x[pair_of_row[row] / pairs_per_token, :], zeros for a row without a pair; 16 bytes a thread
+// xs[row, :] = x[pair_of_row[row] / pairs_per_token, :], zeros for a row without a pair; 16 bytes a thread.
+// pair_scale (float32 [pairs] or null): the row is multiplied by its pair's number (a weight on an expert's input).
 __global__ void moe_gather_rows_kernel(const bf16* __restrict__ x, long long ldx, const int* __restrict__ pair_of_row,
-                                       int pairs_per_token, bf16* __restrict__ xs, int rows, int K) {
+                                       int pairs_per_token, bf16* __restrict__ xs, int rows, int K,
+                                       const float* __restrict__ pair_scale) {
   pdl_wait();
   pdl_trigger();
   const int vecs = K / 8;
@@ -155,6 +162,15 @@ __global__ void moe_gather_rows_kernel(const bf16* __restrict__ x, long long ldx
     const int pair = pair_of_row[row];
     uint4 v = make_uint4(0, 0, 0, 0);
     if (pair >= 0) v = *reinterpret_cast<const uint4*>(x + (size_t)(pair / pairs_per_token) * ldx + c * 8);
+    if (pair >= 0 && pair_scale) {
+      const float w = pair_scale[pair];
+      __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        h2[e] = __floats2bfloat162_rn(f.x * w, f.y * w);
+      }
+    }
     *reinterpret_cast<uint4*>(xs + (size_t)row * K + c * 8) = v;
   }
 }
@@ -184,7 +200,8 @@ template <typename TA, typename TW, typename TO, bool GLU>
 __global__ void __launch_bounds__(256)
 moe_grouped_simt_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ pair_of_row, int pairs_per_token,
                         const TW* __restrict__ W, TO* __restrict__ C, long long ldc, const int* __restrict__ offsets,
-                        const int* __restrict__ tiles, int E, int N, int K, int interleaved, float limit, float alpha) {
+                        const int* __restrict__ tiles, int E, int N, int K, int interleaved, float limit, float alpha,
+                        const float* __restrict__ pair_scale) {
   pdl_wait();
   pdl_trigger();
   __shared__ float As[GBK][kTile + 4];
@@ -246,11 +263,12 @@ moe_grouped_simt_kernel(const TA* __restrict__ A, long long lda, const int* __re
   for (int i = 0; i < 4; ++i) {
     const int row = row0 + tm + i;
     if (row >= row_end) continue;
+    const float ws = (GLU && pair_scale) ? pair_scale[pair_of_row ? pair_of_row[row] : row] : 1.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tn + j;
       if (n >= N) continue;
-      const float v = GLU ? clamped_glu(acc[i][j], acu[GLU ? i : 0][j], limit, alpha) : acc[i][j];
+      const float v = GLU ? clamped_glu(acc[i][j] * ws, acu[GLU ? i : 0][j] * ws, limit, alpha) : acc[i][j];
       C[(size_t)row * ldc + n] = from_float<TO>(v);
     }
   }
@@ -284,7 +302,8 @@ template <typename TO, bool GLU>
 __global__ void __launch_bounds__(256)
 moe_grouped_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ pair_of_row, int pairs_per_token,
                        const bf16* __restrict__ W, TO* __restrict__ C, long long ldc, const int* __restrict__ offsets,
-                       const int* __restrict__ tiles, int E, int NW, int K, float limit, float alpha) {
+                       const int* __restrict__ tiles, int E, int NW, int K, float limit, float alpha,
+                       const float* __restrict__ pair_scale) {
   pdl_wait();
   pdl_trigger();
   // NW: weight rows per expert (twice the features when GLU)
@@ -357,14 +376,15 @@ moe_grouped_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __r
       const int row = row0 + wm * 32 + i * 16 + (lane >> 2) + 8 * half;
       if (row >= row_end) continue;
       if (GLU) {
+        const float ws = pair_scale ? pair_scale[pair_of_row ? pair_of_row[row] : row] : 1.f;
 #pragma unroll
         for (int j2 = 0; j2 < 2; ++j2)
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             const int f = (n0 + wn * 32 + j2 * 16) / 2 + (lane & 3) * 2 + c;
             if (2 * f < NW)
-              C[(size_t)row * ldc + f] = from_float<TO>(clamped_glu(acc[i][2 * j2][2 * half + c], acc[i][2 * j2 + 1][2 * half + c],
-                                                                    limit, alpha));
+              C[(size_t)row * ldc + f] = from_float<TO>(clamped_glu(acc[i][2 * j2][2 * half + c] * ws,
+                                                                    acc[i][2 * j2 + 1][2 * half + c] * ws, limit, alpha));
           }
       } else {
 #pragma unroll
@@ -378,7 +398,8 @@ moe_grouped_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __r
     }
 }
 
-// out[t, :] = sum_c weight[t, c] * rows[row_of_pair[t * top + c], :]  (+ shared[t, :]), float32 sums in the order of c
+// out[t, :] = sum_c weight[t, c] * rows[row_of_pair[t * top + c], :]  (+ shared[t, :]), float32 sums in the order of c;
+// weight null: the rows as they are (the weights went into the experts' inputs)
 template <typename TR, typename TA>
 __global__ void moe_combine_kernel(const TR* __restrict__ rows, long long ldr, const int* __restrict__ row_of_pair,
                                    const float* __restrict__ weight, const TA* __restrict__ shared, TA* __restrict__ out,
@@ -390,7 +411,7 @@ __global__ void moe_combine_kernel(const TR* __restrict__ rows, long long ldr, c
     float acc = 0.f;
     for (int c = 0; c < top; ++c) {
       const int row = row_of_pair[(size_t)t * top + c];
-      if (row >= 0) acc += weight[(size_t)t * top + c] * to_float(rows[(size_t)row * ldr + h]);
+      if (row >= 0) acc += (weight ? weight[(size_t)t * top + c] : 1.f) * to_float(rows[(size_t)row * ldr + h]);
     }
     if (shared) acc += to_float(shared[(size_t)t * H + h]);
     out[(size_t)t * H + h] = from_float<TA>(acc);
@@ -416,15 +437,16 @@ using namespace srlm;
 extern "C" int srlm_moe_tile_rows() { return kTile; }
 
 // logits float32 [T, ld >= E]; bias float32 [E] or null; choice int32 [T, top]; weight float32 [T, top]
+// scoring 0: weights = softmax over the chosen logits; 1: the logistic of each chosen logit
 extern "C" int srlm_moe_route(const float* logits, long long ld, const float* bias, int T, int E, int top, int* choice,
-                              float* weight, cudaStream_t stream) {
+                              float* weight, int scoring, cudaStream_t stream) {
   if (T <= 0) return ST_OK;
-  if (E <= 0 || top <= 0 || top > E || ld < E || E > 8192)
+  if (E <= 0 || top <= 0 || top > E || ld < E || E > 8192 || scoring < 0 || scoring > 1)
     return refuse(ST_BAD_SIZE, "moe_route: experts=%d top=%d ld=%lld (at most 8192 experts)", E, top, ld);
   int warps = 4;
   while (warps > 1 && (size_t)warps * E * sizeof(float) > 40 * 1024) warps >>= 1;
   launch_pdl(moe_route_kernel, dim3((T + warps - 1) / warps), dim3(warps * 32), (size_t)warps * E * sizeof(float), stream,
-             logits, ld, bias, T, E, top, choice, weight);
+             logits, ld, bias, T, E, top, choice, weight, scoring);
   return launched();
 }
 
@@ -438,7 +460,7 @@ extern "C" int srlm_moe_sort_routes(int tokens, int E) { return tokens <= 512 &&
 
 extern "C" int srlm_moe_sort(int* choice, int n, int E, int* offsets, int* tiles, int* pair_of_row,
                              int* row_of_pair, int tile_rows, int* group_of_tile, int max_tiles, int rows_cap,
-                             const float* logits, long long ld, const float* bias, int top, float* weight,
+                             const float* logits, long long ld, const float* bias, int top, float* weight, int scoring,
                              cudaStream_t stream) {
   if (n <= 0) return ST_OK;
   if (E <= 0 || E > 4096) return refuse(ST_BAD_SIZE, "moe_sort: experts=%d (at most 4096)", E);
@@ -452,20 +474,20 @@ extern "C" int srlm_moe_sort(int* choice, int n, int E, int* offsets, int* tiles
   const size_t smem = (size_t)(2 * E + 1) * sizeof(int) + (logits ? (size_t)32 * E * sizeof(float) : 0);
   launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), smem, stream, choice, n, E,
              align ? tile_rows : kTile, align, offsets, tiles, pair_of_row, row_of_pair, group_of_tile, max_tiles, rows_cap,
-             logits, ld, bias, top, weight);
+             logits, ld, bias, top, weight, scoring);
   return launched();
 }
 
 // xs [rows, K] bfloat16 = the rows of x [tokens, ldx] that pair_of_row names (pair / pairs_per_token), zeros for -1
 extern "C" int srlm_moe_gather_rows(const void* x, long long ldx, const int* pair_of_row, int pairs_per_token, void* xs,
-                                    int rows, int K, cudaStream_t stream) {
+                                    int rows, int K, const float* pair_scale, cudaStream_t stream) {
   if (rows <= 0) return ST_OK;
   if (K <= 0 || K % 8 || ldx % 8 || pairs_per_token <= 0 || ((((uintptr_t)x | (uintptr_t)xs) & 15) != 0))
     return refuse(ST_BAD_SIZE, "moe_gather_rows: K=%d ldx=%lld (multiples of 8, 16-byte aligned)", K, ldx);
   const long long total = (long long)rows * (K / 8);
   long long g = (total + 255) / 256;
   launch_pdl(moe_gather_rows_kernel, dim3((unsigned)(g > 148 * 16 ? 148 * 16 : g)), dim3(256), 0, stream, (const bf16*)x, ldx,
-             pair_of_row, pairs_per_token, (bf16*)xs, rows, K);
+             pair_of_row, pairs_per_token, (bf16*)xs, rows, K, pair_scale);
   return launched();
 }
 
@@ -480,7 +502,7 @@ static inline int tile_bound(int n, int E) {
 extern "C" int srlm_moe_grouped_simt(const void* A, int a_dtype, long long lda, const int* pair_of_row, int pairs_per_token,
                                      const void* W, int w_dtype, void* C, int c_dtype, long long ldc, const int* offsets,
                                      const int* tiles, int n, int E, int N, int K, int glu, int interleaved, float limit,
-                                     float alpha, cudaStream_t stream) {
+                                     float alpha, const float* pair_scale, cudaStream_t stream) {
   if (n <= 0) return ST_OK;
   if (E <= 0 || N <= 0 || K <= 0 || lda < K || ldc < N || (pair_of_row && pairs_per_token <= 0) ||
       (glu && interleaved && N % 8))
@@ -492,10 +514,10 @@ extern "C" int srlm_moe_grouped_simt(const void* A, int a_dtype, long long lda, 
   do {                                                                                                                \
     if (glu) launch_pdl(moe_grouped_simt_kernel<TA, TW, TO, true>, grid, dim3(256), 0, stream, (const TA*)A, lda,    \
                         pair_of_row, pairs_per_token, (const TW*)W, (TO*)C, ldc, offsets, tiles, E, N, K, interleaved, \
-                        limit, alpha);                                                                                \
+                        limit, alpha, pair_scale);                                                                    \
     else launch_pdl(moe_grouped_simt_kernel<TA, TW, TO, false>, grid, dim3(256), 0, stream, (const TA*)A, lda,       \
                     pair_of_row, pairs_per_token, (const TW*)W, (TO*)C, ldc, offsets, tiles, E, N, K, interleaved,    \
-                    limit, alpha);                                                                                    \
+                    limit, alpha, pair_scale);                                                                        \
   } while (0)
   if (a_dtype == DT_F32 && w_dtype == DT_F32 && c_dtype == DT_F32) SRLM_GROUPED(float, float, float);
   else if (a_dtype == DT_BF16 && w_dtype == DT_BF16 && c_dtype == DT_BF16) SRLM_GROUPED(bf16, bf16, bf16);
@@ -547,7 +569,8 @@ extern "C" int srlm_moe_grouped_mma_takes(int N, int K, int glu) { return K > 0 
 
 extern "C" int srlm_moe_grouped_mma(const void* A, long long lda, const int* pair_of_row, int pairs_per_token, const void* W,
                                     void* C, int c_dtype, long long ldc, const int* offsets, const int* tiles, int n, int E,
-                                    int N, int K, int glu, float limit, float alpha, cudaStream_t stream) {
+                                    int N, int K, int glu, float limit, float alpha, const float* pair_scale,
+                                    cudaStream_t stream) {
   if (n <= 0) return ST_OK;
   if (E <= 0 || !srlm_moe_grouped_mma_takes(N, K, glu) || lda < K || lda % 8 || ldc < N || (pair_of_row && pairs_per_token <= 0))
     return refuse(ST_BAD_SIZE, "moe_grouped_mma: experts=%d N=%d K=%d lda=%lld ldc=%lld", E, N, K, lda, ldc);
@@ -558,7 +581,7 @@ extern "C" int srlm_moe_grouped_mma(const void* A, long long lda, const int* pai
   dim3 grid((NW + MBN - 1) / MBN, bound);
 #define SRLM_GROUPED_MMA(TO, G)                                                                                          \
   launch_pdl(moe_grouped_mma_kernel<TO, G>, grid, dim3(256), 0, stream, (const bf16*)A, lda, pair_of_row, pairs_per_token, \
-             (const bf16*)W, (TO*)C, ldc, offsets, tiles, E, NW, K, limit, alpha)
+             (const bf16*)W, (TO*)C, ldc, offsets, tiles, E, NW, K, limit, alpha, pair_scale)
   if (c_dtype == DT_BF16 && glu) SRLM_GROUPED_MMA(bf16, true);
   else if (c_dtype == DT_F32 && glu) SRLM_GROUPED_MMA(float, true);
   else if (c_dtype == DT_BF16) SRLM_GROUPED_MMA(bf16, false);

@@ -159,6 +159,15 @@ class KernelLibrary:
         self._check(self.lib.srlm_cast(_ptr(src), dtype_code(src.dtype), _ptr(dst), dtype_code(dst.dtype),
                                        C.c_longlong(src.numel()), _stream()), "cast")
 
+    def cast_columns(self, src, column, dst):
+        """dst [T, width] (contiguous, float32 or bfloat16) = the float32 columns [column, column + width) of src."""
+        T, width = dst.shape
+        if src.dtype != torch.float32 or src.stride(1) != 1 or src.shape[1] < column + width or src.shape[0] != T:
+            raise ShapeError("cast_columns: float32 columns of a row-major tensor")
+        self._check(self.lib.srlm_cast_columns(C.c_void_p(src.data_ptr() + 4 * column), C.c_longlong(src.stride(0)),
+                                               _ptr(dst), dtype_code(dst.dtype), C.c_int(T), C.c_int(width), _stream()),
+                    "cast_columns")
+
     def patch_words(self, words, pairs, src, n, flag):
         """words[pairs[2 i]] = src[pairs[2 i + 1]] for i < n, all int32 on the device: token ids that a step
         takes from what the step before it sampled, before the host has read them.  An index outside its
@@ -184,6 +193,14 @@ class KernelLibrary:
         T, half = cos.shape
         self._check(self.lib.srlm_rope_table(_ptr(positions), _ptr(cos), _ptr(sin), C.c_int(T), C.c_int(half),
                                              C.c_double(theta), C.c_int(rotary_dim), _stream()), "rope_table")
+
+    def rope_table_freq(self, positions, freq, cos, sin):
+        """cos / sin [T, half] of position * freq[i]; freq float64 [half] on the device."""
+        T, half = cos.shape
+        if freq.dtype != torch.float64 or freq.numel() != half:
+            raise ShapeError("rope_table_freq: one float64 frequency per pair")
+        self._check(self.lib.srlm_rope_table_freq(_ptr(positions), _ptr(freq), _ptr(cos), _ptr(sin), C.c_int(T),
+                                                  C.c_int(half), _stream()), "rope_table_freq")
 
     def qk_norm_rope_append(self, qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, eps, cos, sin, kv_slot,
                             nq, nkv, hd, rotary_half, write_kv=True, interleaved=False):
@@ -480,13 +497,14 @@ class KernelLibrary:
         (a multiple of 128), a block each, added by a second kernel; part_o float32
         [n * 2 * nkv * nsplit * 128, 128] and part_ml [.., 2] are their workspace."""
         err = self._gemm_state(q.device)[1]
-        if mods is not None:        # (head_scale, pen_weight, pen_rate), float32 [nq] each or None: see paged_attention_general
+        if mods is not None:        # (head_scale, pen_weight, pen_rate[, softcap]): float32 [nq] each or None, and a number; see paged_attention_general
             self._check(self.lib.srlm_paged_attention_prefill_tcgen05_mods(
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), C.c_longlong(k_cache.shape[0]), _ptr(block_table),
                 C.c_int(block_table.stride(0)), _ptr(cu_q), _ptr(kv_lens), _ptr(work), C.c_int(work.shape[0]),
                 C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(page_size), C.c_float(scale), C.c_int(window or 0),
                 C.c_int(tiles_per_block), C.c_int(nsplit), C.c_int(kv_chunk), _ptr(part_o), _ptr(part_ml), _ptr(sinks),
-                _ptr(mods[0]), _ptr(mods[1]), _ptr(mods[2]), _ptr(err), _stream()), "paged_attention_prefill_tcgen05")
+                _ptr(mods[0]), _ptr(mods[1]), _ptr(mods[2]), C.c_float(mods[3] if len(mods) > 3 and mods[3] else 0.0),
+                _ptr(err), _stream()), "paged_attention_prefill_tcgen05")
         elif sinks is not None:     # float32 [nq]: one more term exp(sink) in each head's softmax denominator
             self._check(self.lib.srlm_paged_attention_prefill_tcgen05_sinks(
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), C.c_longlong(k_cache.shape[0]), _ptr(block_table),
@@ -789,13 +807,14 @@ class KernelLibrary:
     GENERAL_ROWS = 16        # rows (tokens x query heads of a KV head) of a block of the general attention kernel
 
     def paged_attention_general(self, ctx, q, k_cache, v_cache, out, block_table, sinks, nq, nkv, dk, dv, scale,
-                                window=0, head_scale=None, penalty=None, gate=None):
+                                window=0, head_scale=None, penalty=None, gate=None, softcap=None):
         """Causal attention of the batch of ``ctx`` over pages whose keys have dk and whose values have dv
         elements (v_cache None: the values are the keys' first dv elements).  q float32 [T, nq * dk];
         k_cache [pages, nkv, page_size, dk]; out [T, nq * dv], float32 or the cache's dtype; sinks float32
         [nq] or None: one more term exp(sink) in each head's softmax denominator.  head_scale float32 [nq] or
         None: a factor per head on the scaled scores.  penalty (weight, rate), float32 [nq] each, or None:
-        weight * ln(1 + rate * distance to the key) is taken off the score.  window > 0: a query sees itself
+        weight * ln(1 + rate * distance to the key) is taken off the score.  softcap (a number) or None: the scaled
+        score s becomes softcap * tanh(s / softcap), ahead of the penalty.  window > 0: a query sees itself
         and the window - 1 keys before it.  gate (float32 tensor [T, >= column + nq], column) or None: head h of
         token t is multiplied by the logistic of tensor[t, column + h] as it is written.
 
@@ -808,7 +827,8 @@ class KernelLibrary:
             raise ShapeError("paged_attention_general: float32 queries")
         n = ctx.n_entries
         g = nq // nkv
-        mods = (_ptr(head_scale), _ptr(penalty[0] if penalty else None), _ptr(penalty[1] if penalty else None))
+        mods = (_ptr(head_scale), _ptr(penalty[0] if penalty else None), _ptr(penalty[1] if penalty else None),
+                C.c_float(softcap or 0.0))
         if gate is not None:
             logits, column = gate
             if logits.dtype != torch.float32 or not logits.is_cuda or logits.stride(1) != 1 or logits.shape[1] < column + nq:
@@ -877,17 +897,21 @@ class KernelLibrary:
             self.launches += 1           # the kernel that adds the slices
 
     def attention_bias_append(self, proj, bias, q_out, k_cache, v_cache, kv_slot, nq, nkv, dk, dv, v_keep=None,
-                              lam=None, mix_mode=0, write_kv=True):
+                              lam=None, mix_mode=0, write_kv=True, rotation=None):
         """From a stacked q | k | v projection [T, >= nq dk + nkv (dk + dv)]: q + bias to q_out (float32, or
         bfloat16 for the kernels that take their queries so), k + bias
         and v + bias to the pages.  mix_mode 1 also keeps v in v_keep (float32 [T, nkv dv]); mix_mode 2 writes
-        (1 - lam) v + lam v_keep instead of v (lam: float32 [1] on the device)."""
+        (1 - lam) v + lam v_keep instead of v (lam: float32 [1] on the device).  rotation (parts.base.Rotation) or
+        None: the first 2 * pairs elements of every q and k head are turned, behind the bias, by the step's angles.
+        write_kv False without value mixing: proj holds the q columns alone."""
         T = proj.shape[0]
+        pairs = rotation.pairs if rotation is not None else 0
         self._check(self.lib.srlm_attention_bias_append(
             _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), _ptr(bias), _ptr(q_out),
             dtype_code(q_out.dtype), _ptr(k_cache), _ptr(v_cache), dtype_code(k_cache.dtype), _ptr(kv_slot), _ptr(v_keep), _ptr(lam), C.c_int(mix_mode),
             C.c_int(int(write_kv)), C.c_int(T), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv),
-            C.c_int(k_cache.shape[2]), _stream()), "attention_bias_append")
+            C.c_int(k_cache.shape[2]), _ptr(rotation.cos if pairs else None), _ptr(rotation.sin if pairs else None),
+            C.c_int(pairs), C.c_int(int(bool(pairs and rotation.interleaved))), _stream()), "attention_bias_append")
 
     def attention_unit_norm_append(self, proj, eps, q_out, k_cache, v_cache, kv_slot, nq, nkv, dk, dv, write_kv=True):
         """From a stacked q | k | v (| more) projection [T, >= nq dk + nkv (dk + dv)]: every q and k head divided by
@@ -915,9 +939,12 @@ class KernelLibrary:
             raise ShapeError("float32 columns of a row-major CUDA tensor are wanted")
         return C.c_void_p(t.data_ptr() + 4 * column), C.c_longlong(t.stride(0))
 
-    def moe_route(self, logits, bias, top, choice, weight, column=0, experts=None):
+    ROUTER_SCORING = {"softmax_of_chosen": 0, "logistic": 1}
+
+    def moe_route(self, logits, bias, top, choice, weight, column=0, experts=None, scoring="softmax_of_chosen"):
         """logits float32 [T, E] (+ bias float32 [E]) -> choice int32 [T, top], the experts with the largest
-        logits (ties: the lowest index), and weight float32 [T, top], the softmax over the chosen logits.
+        logits (ties: the lowest index), and weight float32 [T, top]: the softmax over the chosen logits, or
+        (scoring "logistic") the logistic of each chosen logit, not renormalised.
         column / experts: the logits are those columns of a wider tensor."""
         T = logits.shape[0]
         E = logits.shape[1] - column if experts is None else experts
@@ -925,14 +952,15 @@ class KernelLibrary:
             raise ShapeError("moe_route: float32 logits and weights, int32 choices")
         ptr, ld = self._columns(logits, column, E)
         self._check(self.lib.srlm_moe_route(ptr, ld, _ptr(bias), C.c_int(T), C.c_int(E),
-                                            C.c_int(top), _ptr(choice), _ptr(weight), _stream()), "moe_route")
+                                            C.c_int(top), _ptr(choice), _ptr(weight),
+                                            C.c_int(self.ROUTER_SCORING[scoring]), _stream()), "moe_route")
 
     def moe_sort_routes(self, tokens, experts) -> bool:
         """Whether moe_sort(..., route=...) routes a step of this many tokens itself."""
         return bool(self.lib.srlm_moe_sort_routes(C.c_int(tokens), C.c_int(experts)))
 
     def moe_sort(self, choice, experts, offsets, tiles, pair_of_row, row_of_pair, tile_rows=0, group_of_tile=None,
-                 route=None):
+                 route=None, scoring="softmax_of_chosen"):
         """The (token, choice) pairs ordered by expert: offsets / tiles int32 [experts + 1] (first row and first
         tile of each expert), pair_of_row / row_of_pair int32 [pairs].  tile_rows > 0: every expert's rows start at
         a multiple of tile_rows; pair_of_row then covers all rows of group_of_tile's tiles (-1: a row without a
@@ -948,7 +976,7 @@ class KernelLibrary:
             _ptr(choice), C.c_int(choice.numel()), C.c_int(experts), _ptr(offsets), _ptr(tiles), _ptr(pair_of_row),
             _ptr(row_of_pair), C.c_int(tile_rows), _ptr(group_of_tile),
             C.c_int(group_of_tile.numel() if group_of_tile is not None else 0),
-            C.c_int(pair_of_row.numel()), *routing, _stream()), "moe_sort")
+            C.c_int(pair_of_row.numel()), *routing, C.c_int(self.ROUTER_SCORING[scoring]), _stream()), "moe_sort")
 
     GROUPED_TILE = 128       # token rows of a tile of the grouped tensor-memory product (one SM a tile)
     GROUPED_PAIR_TILE = 256  # ... of its pair form (two SMs on 256 weight rows x 256 tokens)
@@ -962,11 +990,12 @@ class KernelLibrary:
         big = pairs >= 512 * experts and weight_elements >= 16 << 20
         return self.GROUPED_PAIR_TILE if self.grouped_pairs and big else self.GROUPED_TILE
 
-    def moe_gather_rows(self, x, pair_of_row, pairs_per_token, out):
-        """out[row] = x[pair_of_row[row] // pairs_per_token] (bfloat16 rows; zeros where pair_of_row is -1)."""
+    def moe_gather_rows(self, x, pair_of_row, pairs_per_token, out, pair_scale=None):
+        """out[row] = x[pair_of_row[row] // pairs_per_token] (bfloat16 rows; zeros where pair_of_row is -1), times
+        pair_scale[pair] (float32, one number a pair) when given."""
         self._check(self.lib.srlm_moe_gather_rows(_ptr(x), C.c_longlong(x.stride(0)), _ptr(pair_of_row),
                                                   C.c_int(pairs_per_token), _ptr(out), C.c_int(out.shape[0]),
-                                                  C.c_int(out.shape[1]), _stream()), "moe_gather_rows")
+                                                  C.c_int(out.shape[1]), _ptr(pair_scale), _stream()), "moe_gather_rows")
 
     def gemm_tn_tcgen05_grouped(self, x, w, out, group_of_tile, glu=False, limit=0.0, alpha=0.0, tile_rows=128):
         """out[r] = x[r] . w[group of r's tile]^T on the persistent tensor-memory kernel: x [rows, K] bfloat16 in tiles
@@ -984,10 +1013,13 @@ class KernelLibrary:
             C.c_float(limit), C.c_float(alpha), _ptr(err), _stream()), "gemm_tn_tcgen05_grouped")
 
     def moe_grouped(self, a, pair_of_row, pairs_per_token, w, out, offsets, tiles, glu=False, interleaved=False,
-                    limit=0.0, alpha=0.0):
+                    limit=0.0, alpha=0.0, pair_scale=None):
         """out[row] = a[row's token] . w[row's expert]^T for every row of the sorted pairs (pair_of_row None: row r
         of ``a`` is row r of ``out``).  w [experts, N, K]; glu: w [experts, 2 N, K] and out gets the clamped GLU of
-        the gate and up halves (interleaved: in blocks of 8 gate rows and 8 up rows, else all gate rows first)."""
+        the gate and up halves (interleaved: in blocks of 8 gate rows and 8 up rows, else all gate rows first);
+        limit 0: the plain GLU, gate * logistic(gate) * up.  pair_scale (float32, one number a pair; with glu): the
+        gate and up sums of a row are multiplied by its pair's number ahead of the activation, which for experts
+        without biases is the activation of the scaled input."""
         E, rows, K = w.shape
         n, N = out.shape
         if a.shape[1] != K or rows != (2 * N if glu else N):
@@ -998,21 +1030,22 @@ class KernelLibrary:
             self._check(self.lib.srlm_moe_grouped_mma(
                 _ptr(a), C.c_longlong(a.stride(0)), _ptr(pair_of_row), C.c_int(pairs_per_token), _ptr(w), _ptr(out),
                 dtype_code(out.dtype), C.c_longlong(out.stride(0)), _ptr(offsets), _ptr(tiles), C.c_int(n), C.c_int(E),
-                C.c_int(N), C.c_int(K), C.c_int(int(glu)), C.c_float(limit), C.c_float(alpha), _stream()),
+                C.c_int(N), C.c_int(K), C.c_int(int(glu)), C.c_float(limit), C.c_float(alpha), _ptr(pair_scale), _stream()),
                 "moe_grouped_mma")
             return
         self._check(self.lib.srlm_moe_grouped_simt(
             _ptr(a), dtype_code(a.dtype), C.c_longlong(a.stride(0)), _ptr(pair_of_row), C.c_int(pairs_per_token), _ptr(w),
             dtype_code(w.dtype), _ptr(out), dtype_code(out.dtype), C.c_longlong(out.stride(0)), _ptr(offsets), _ptr(tiles),
             C.c_int(n), C.c_int(E), C.c_int(N), C.c_int(K), C.c_int(int(glu)), C.c_int(int(interleaved)), C.c_float(limit),
-            C.c_float(alpha), _stream()), "moe_grouped_simt")
+            C.c_float(alpha), _ptr(pair_scale), _stream()), "moe_grouped_simt")
 
     def moe_combine(self, rows, row_of_pair, weight, shared, out):
-        """out[t] = sum over t's choices, in their order, of weight * rows[row of the pair] (+ shared[t])."""
+        """out[t] = sum over t's choices, in their order, of weight * rows[row of the pair] (+ shared[t]); weight
+        None: the rows as they are; row_of_pair int32 [T, top]."""
         T, H = out.shape
         self._check(self.lib.srlm_moe_combine(
             _ptr(rows), dtype_code(rows.dtype), C.c_longlong(rows.stride(0)), _ptr(row_of_pair), _ptr(weight), _ptr(shared),
-            _ptr(out), dtype_code(out.dtype), C.c_int(T), C.c_int(weight.shape[1]), C.c_int(H), _stream()), "moe_combine")
+            _ptr(out), dtype_code(out.dtype), C.c_int(T), C.c_int(row_of_pair.numel() // T), C.c_int(H), _stream()), "moe_combine")
 
     def clamped_glu(self, gate_up, out, limit, alpha):
         """out [T, F] = g * logistic(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); gate_up
@@ -1022,6 +1055,37 @@ class KernelLibrary:
                                               _ptr(out), dtype_code(out.dtype),
                                               C.c_int(T), C.c_int(F), C.c_float(limit), C.c_float(alpha), _stream()),
                     "clamped_glu")
+
+    # ---- the selective scan ---------------------------------------------------------------------
+    def scan_conv(self, ctx, xz, conv_w, conv_b, state, x_out, x_low, channels, N, taps):
+        """x_out float32 [T, channels] = silu(causal convolution over time of xz's first ``channels`` columns + conv_b);
+        the inputs ahead of an entry's first token are the slot's carried ones (state [slots, channels * (N + taps - 1)]:
+        S, then the last taps - 1 inputs of every channel).  x_low: a second copy in bfloat16, or None."""
+        self._check(self.lib.srlm_scan_conv(
+            _ptr(xz), C.c_longlong(xz.stride(0)), _ptr(conv_w), _ptr(conv_b), _ptr(state), C.c_longlong(state.stride(0)),
+            _ptr(ctx.entry_of_token), _ptr(ctx.cu_q), _ptr(ctx.slots), _ptr(x_out), _ptr(x_low),
+            dtype_code(x_low.dtype) if x_low is not None else DT_F32, C.c_int(xz.shape[0]), C.c_int(channels), C.c_int(N),
+            C.c_int(taps), _stream()), "scan_conv")
+
+    def selective_scan(self, ctx, x, xz, dbc, b_off, dt_raw, dt_bias, A, D, state, out, channels, N, taps):
+        """Token by token in every entry: dt = softplus(dt_raw + dt_bias); S <- exp(dt A) S + dt x B; out = (S C + D x)
+        silu(z).  x, dt_raw float32 [T, channels]; xz float32 [T, >= 2 channels] (inputs of the convolution, then z);
+        dbc float32 rows with B in columns [b_off, b_off + N) and C behind them; A float32 [channels, N]; the slots'
+        S and carried inputs in ``state`` are renewed."""
+        self._check(self.lib.srlm_selective_scan(
+            _ptr(x), _ptr(xz), C.c_longlong(xz.stride(0)), _ptr(dbc), C.c_longlong(dbc.stride(0)), C.c_int(b_off),
+            _ptr(dt_raw), _ptr(dt_bias), _ptr(A), _ptr(D), _ptr(state), C.c_longlong(state.stride(0)), _ptr(ctx.cu_q),
+            _ptr(ctx.slots), _ptr(out), dtype_code(out.dtype), C.c_int(ctx.n_entries), C.c_int(channels), C.c_int(N),
+            C.c_int(taps), _stream()), "selective_scan")
+
+    def paired_rmsnorm_mean(self, a, wa, b, wb, eps, out):
+        """out = (wa * rms_norm(a) + wb * rms_norm(b)) / 2, rows of [T, H]; a and b of one dtype."""
+        T, H = out.shape
+        if a.dtype != b.dtype or tuple(a.shape) != (T, H) or tuple(b.shape) != (T, H):
+            raise ShapeError(f"paired_rmsnorm_mean: a {tuple(a.shape)} {a.dtype}, b {tuple(b.shape)} {b.dtype}")
+        self._check(self.lib.srlm_paired_rmsnorm_mean(_ptr(a), _ptr(wa), _ptr(b), _ptr(wb), C.c_float(eps), _ptr(out),
+                                                      dtype_code(a.dtype), dtype_code(out.dtype), C.c_int(T), C.c_int(H),
+                                                      _stream()), "paired_rmsnorm_mean")
 
     # ---- attention over a cached latent ----------------------------------------------------
     def latent_append(self, proj, c_off, norm_w, eps, rotation, cache, kv_slot, rank, rot):

@@ -1,6 +1,6 @@
 """The parts a model is assembled from.  Importing the package registers the built-in kinds."""
 from . import (attention, block, delta_rule, distance_attention, feedforward, latent_attention, norm,  # noqa: F401
-               position, routed_experts, sink_attention)
+               position, rotated_attention, routed_experts, selective_scan, side_by_side, sink_attention)
 from .base import (BLOCKS, Block, EMBEDDING, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, ROTATION,  # noqa: F401
                    CacheNeed, ModelContext, Rotation, Part, StepContext, Workspace, register_block, register_feed_forward,
                    register_mixer, register_norm, register_position_encoding)

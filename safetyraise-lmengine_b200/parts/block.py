@@ -2,6 +2,7 @@
 
 ``pre_norm``: r = x + mixer(norm(x)); x' = r + ff(norm(r))  (src/model/native.rs:526-562).
 ``sandwich_gated``: a norm before and after each sublayer and a learned gate on its result (see the class).
+``parallel``: h = norm(x); x' = x + mixer(h) + ff(h): one norm, both sublayers read it.
 
 The residual stream is a float32 tensor updated in place.  A block does not add
 its feed-forward output itself: it returns it as *pending*, and the next norm
@@ -83,6 +84,49 @@ class PreNormBlock(Block):
         if self.feed_forward is None:
             return mixed                      # the next norm adds it
         self.ff_norm.apply(residual, mixed, n)
+        return self.feed_forward.forward(ctx, n)
+
+
+@register_block("parallel")
+class ParallelBlock(Block):
+    """One norm whose output both sublayers read; the sum of their results joins the stream:
+
+        h = norm(x);   x <- x + (mixer(h) + ff(h))
+
+    A feed-forward that takes an addend (``takes_addend``) adds the mixer's result where it forms its own;
+    otherwise the mixer's result is added to the stream here and the feed-forward's is left pending."""
+
+    def __init__(self, spec: LayerSpec, tensors: dict, mctx):
+        p = spec.weight_prefix
+        self.spec = spec
+        self.norm = lookup(NORMS, spec.mixer_norm.kind, "norm")(spec.mixer_norm, p + spec.mixer_norm_name, tensors, mctx)
+        self.mixer = lookup(MIXERS, spec.mixer.kind, "mixer")(spec.mixer, p, tensors, mctx)
+        self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.feed_forward = lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward")(
+                spec.feed_forward, p, tensors, mctx)
+        self.hidden = spec.mixer_norm.size
+        self.replayable = all(getattr(part, "replayable", True) for part in (self.norm, self.mixer, self.feed_forward))
+
+    @classmethod
+    def tensor_decls(cls, spec: LayerSpec, prefix: str = "") -> List[TensorDecl]:
+        p = spec.weight_prefix
+        decls = (lookup(NORMS, spec.mixer_norm.kind, "norm").tensor_decls(spec.mixer_norm, p + spec.mixer_norm_name)
+                 + lookup(MIXERS, spec.mixer.kind, "mixer").tensor_decls(spec.mixer, p))
+        if spec.feed_forward is not None:
+            decls += lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward").tensor_decls(spec.feed_forward, p)
+        return decls
+
+    def forward(self, ctx, residual, pending, run_step: RunStep, next_block=None):
+        assert not isinstance(pending, NormedInput), "a prepared input was handed to a block that did not ask for one"
+        n = ctx.workspace.get("block.normed", residual.shape[0], self.hidden, ctx.dtype)
+        self.norm.apply(residual, pending, n)
+        mixed = self.mixer.forward(ctx, n, run_step)
+        if self.feed_forward is None:
+            return mixed                      # the next norm adds it
+        if getattr(self.feed_forward, "takes_addend", False):
+            return self.feed_forward.forward(ctx, n, add=mixed)
+        ops.residual_add(residual, mixed)
         return self.feed_forward.forward(ctx, n)
 
 

@@ -39,24 +39,33 @@ def cache_groups_of(spec: ModelSpec) -> List[CacheGroupSpec]:
     """What a model of this specification needs from the cache manager, from the specification alone.
     Run steps with equal needs share a group; each group gets pages (or state) of its own."""
     from .base import MIXERS
-    need_of = lambda step: lookup(MIXERS, spec.layers[step.layer].mixer.kind, "mixer").cache_need_of(
-        spec.layers[step.layer].mixer)
+
+    def needs_of(step):
+        """(need, cache entry) of every mixer of the step: one, or one per mixer of a side-by-side pair."""
+        mixer = spec.layers[step.layer].mixer
+        need = lookup(MIXERS, mixer.kind, "mixer").cache_need_of(mixer)
+        needs = need if isinstance(need, tuple) else (need,)
+        entries = (step.cache,) + tuple(step.more_caches)
+        if len(needs) != len(entries):
+            raise ConfigError(f"a run step of layer {step.layer} names {len(entries)} cache entries for {len(needs)} mixers")
+        return list(zip(needs, entries))
+
     by_need: "OrderedDict[object, list]" = OrderedDict()
     owner_need = {}
     for step in spec.run_order:
-        need = need_of(step)
-        if need.kind == "none":
-            continue
-        if step.writes_cache:
-            if step.cache in owner_need:
-                raise ConfigError(f"cache entry {step.cache} is written by two run steps")
-            owner_need[step.cache] = need
-            by_need.setdefault(need, []).append(step.cache)
+        for need, entry in needs_of(step):
+            if need.kind == "none":
+                continue
+            if step.writes_cache:
+                if entry in owner_need:
+                    raise ConfigError(f"cache entry {entry} is written by two run steps")
+                owner_need[entry] = need
+                by_need.setdefault(need, []).append(entry)
     for step in spec.run_order:
-        need = need_of(step)
-        if need.kind != "none" and not step.writes_cache and owner_need.get(step.cache) != need:
-            raise ConfigError(f"a run step reads cache entry {step.cache}, which no step with the "
-                              f"same needs writes")
+        for need, entry in needs_of(step):
+            if need.kind != "none" and not step.writes_cache and owner_need.get(entry) != need:
+                raise ConfigError(f"a run step reads cache entry {entry}, which no step with the "
+                                  f"same needs writes")
     groups = []
     for i, (need, entries) in enumerate(by_need.items()):
         groups.append(CacheGroupSpec(name=f"g{i}:{need.kind}", kind=need.kind, entries=tuple(entries),

@@ -2,15 +2,37 @@
 
 angle = pos / theta^(2i/rotary_dim); src/model/math.rs:52-99.  ``prepare``
 fills one cos/sin table per step; every mixer that shares the same
-specification reuses it.
+specification reuses it.  A specification with ``scaling`` rescales the
+frequencies by their wavelength (see ``rescaled_frequencies``).
 """
 from __future__ import annotations
+
+import math
 
 import torch
 
 from ..config.spec import PositionSpec
 from ..kernels import ops
 from .base import ROTATION, Part, Rotation, register_position_encoding
+
+
+def rescaled_frequencies(theta: float, rotary_dim: int, scaling) -> list:
+    """f_i = theta^(-2i/rotary_dim) for i < rotary_dim / 2, in double precision; with scaling = (factor, low, high,
+    original) and wavelength l = 2 pi / f: f where l < original / high, f / factor where l > original / low, and
+    between the two (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
+    out = []
+    for i in range(rotary_dim // 2):
+        f = theta ** (-2.0 * i / rotary_dim)
+        if scaling is not None:
+            factor, low, high, original = scaling
+            wave = 2.0 * math.pi / f
+            if wave > original / low:
+                f = f / factor
+            elif wave >= original / high:
+                s = (original / wave - low) / (high - low)
+                f = (1.0 - s) * f / factor + s * f
+        out.append(f)
+    return out
 
 
 @register_position_encoding("rotary_half")
@@ -20,15 +42,23 @@ class RotaryHalf(Part):
     def __init__(self, spec: PositionSpec, mctx):
         self.spec = spec
         self.half = spec.rotary_dim // 2
-        self.key = ("rotary_half", spec.theta, spec.rotary_dim)
+        self.key = ("rotary_half", spec.theta, spec.rotary_dim, spec.scaling)
+        self.freq = None
+        if spec.scaling is not None:
+            self.freq = torch.tensor(rescaled_frequencies(spec.theta, spec.rotary_dim, spec.scaling),
+                                     dtype=torch.float64, device=mctx.device)
 
     def rotation(self, ctx) -> Rotation:
         """The rotation of this step's tokens: cos / sin float32 [T, rotary_dim/2], half-split pairs."""
         got = ctx.tables.get(self.key)
         if got is None:
-            cos = ctx.workspace.get(f"rope.cos.{self.spec.theta}", ctx.T, self.half, torch.float32)
-            sin = ctx.workspace.get(f"rope.sin.{self.spec.theta}", ctx.T, self.half, torch.float32)
-            ops.rope_table(ctx.positions, cos, sin, self.spec.theta, self.spec.rotary_dim)
+            tag = f"{self.spec.theta}" if self.freq is None else f"{self.spec.theta}.{self.spec.scaling}"
+            cos = ctx.workspace.get(f"rope.cos.{tag}", ctx.T, self.half, torch.float32)
+            sin = ctx.workspace.get(f"rope.sin.{tag}", ctx.T, self.half, torch.float32)
+            if self.freq is None:
+                ops.rope_table(ctx.positions, cos, sin, self.spec.theta, self.spec.rotary_dim)
+            else:
+                ops.rope_table_freq(ctx.positions, self.freq, cos, sin)
             got = ctx.tables[self.key] = Rotation(cos, sin, self.half, interleaved=False)
         return got
 
@@ -39,7 +69,7 @@ class RotaryInterleaved(RotaryHalf):
 
     def __init__(self, spec: PositionSpec, mctx):
         super().__init__(spec, mctx)
-        self.key = ("rotary_interleaved", spec.theta, spec.rotary_dim)
+        self.key = ("rotary_interleaved", spec.theta, spec.rotary_dim, spec.scaling)
 
     def rotation(self, ctx) -> Rotation:
         got = ctx.tables.get(self.key)

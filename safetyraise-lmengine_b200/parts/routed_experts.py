@@ -5,6 +5,12 @@
     out = sum_{e in E(h)} w_e * expert_e(h)  +  shared(h)
     expert(h) = W_down (g * logistic(alpha g) * (u + 1)),  g = min(W_gate h, limit),  u = clamp(W_up h, -limit, limit)
 
+Variants by the specification: ``scoring`` "logistic" takes w_e = logistic(z_e), not renormalised; ``activation``
+"silu" is the plain gate * logistic(gate) * up; ``weight_on_input`` computes sum_e expert_e(w_e h) instead: the
+experts have no biases, so W (w h) = w (W h), and the first grouped product multiplies its gate and up sums by
+the pair's weight ahead of the activation (steps of many tokens, whose rows are gathered into tiles, scale the
+gathered rows).
+
 The pairs (token, chosen expert) are ordered by expert on the device and every expert's rows run through
 one grouped product per projection; a token's result does not depend on what else is in the step, and
 nothing is planned on the host, so decode steps replay from CUDA graphs.
@@ -26,9 +32,14 @@ from .linear import Linear
 @register_feed_forward("routed_experts")
 class RoutedExperts(Part):
     def __init__(self, spec: RoutedExpertsSpec, prefix: str, tensors: dict, mctx):
-        if spec.activation != "clamped_glu":
+        if spec.activation not in ("clamped_glu", "silu"):
             raise Unsupported(f"routed experts with activation {spec.activation!r} are not implemented")
+        if spec.scoring not in ops.ROUTER_SCORING:
+            raise Unsupported(f"routed experts with router scoring {spec.scoring!r} are not implemented")
+        if spec.activation == "silu" and spec.shared_size:
+            raise Unsupported("an expert that every token runs comes with the clamped activation only")
         self.spec = spec
+        self.limit = spec.limit if spec.activation == "clamped_glu" else 0.0      # 0: the plain gated activation
         p, nm = prefix, spec.expert_names
         self.router_bias = tensors[p + nm.router_bias] if spec.router_bias else None
         each = lambda part: [tensors[p + nm.expert.format(e) + part] for e in range(spec.experts)]
@@ -73,11 +84,15 @@ class RoutedExperts(Part):
                       TensorDecl(sp + nm.down, (H, s.shared_size), MATRIX)]
         return decls
 
-    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+    takes_addend = True       # forward(..., add=...) adds a tensor of the output's shape and dtype in the combination
+
+    def forward(self, ctx, x: torch.Tensor, add=None) -> torch.Tensor:
         s = self.spec
         T, H = x.shape
         ws = ctx.workspace
         pairs = T * s.top
+        if add is not None and self.shared_down is not None:
+            raise Unsupported("routed experts add either their shared expert's output or a given tensor")
         # the router in float32: its input may be the activation dtype's rounding of the normed stream
         first = self.first(ctx, x, "moe.first", out_dtype=torch.float32)
         choice = ws.get("moe.choice", T, s.top, torch.int32)
@@ -86,25 +101,28 @@ class RoutedExperts(Part):
         # kernel, every expert's rows in whole tiles of 128 of a gathered copy of the input
         if (self.interleaved and ops.grouped_products_in_tensor_memory and pairs >= 64 * s.experts
                 and s.intermediate_size % 8 == 0):
-            ops.moe_route(first, self.router_bias, s.top, choice, weight, column=self.router_column, experts=s.experts)
-            return self._forward_tiles(ctx, x, first, choice, weight)
+            ops.moe_route(first, self.router_bias, s.top, choice, weight, column=self.router_column, experts=s.experts,
+                          scoring=s.scoring)
+            return self._forward_tiles(ctx, x, first, choice, weight, add)
         heads = ws.get("moe.heads", 2, s.experts + 1, torch.int32, reserve=2)
         order = ws.get("moe.order", 2 * T, s.top, torch.int32, reserve=2 * ws.max_tokens)
         offsets, tiles = heads[0], heads[1]
         pair_of_row, row_of_pair = order[:T].view(-1), order[T:].view(-1)
         if ops.moe_sort_routes(T, s.experts):          # a small step: the block that orders the pairs routes them too
             ops.moe_sort(choice, s.experts, offsets, tiles, pair_of_row, row_of_pair,
-                         route=(first, self.router_column, self.router_bias, weight))
+                         route=(first, self.router_column, self.router_bias, weight), scoring=s.scoring)
         else:
-            ops.moe_route(first, self.router_bias, s.top, choice, weight, column=self.router_column, experts=s.experts)
+            ops.moe_route(first, self.router_bias, s.top, choice, weight, column=self.router_column, experts=s.experts,
+                          scoring=s.scoring)
             ops.moe_sort(choice, s.experts, offsets, tiles, pair_of_row, row_of_pair)
         y = ws.get("moe.y", pairs, s.intermediate_size, ctx.dtype, reserve=ws.max_tokens * s.top)
         ops.moe_grouped(x, pair_of_row, s.top, self.gate_up, y, offsets, tiles, glu=True, interleaved=self.interleaved,
-                        limit=s.limit, alpha=s.glu_alpha)
+                        limit=self.limit, alpha=s.glu_alpha, pair_scale=weight if s.weight_on_input else None)
         rows = ws.get("moe.rows", pairs, H, torch.float32, reserve=ws.max_tokens * s.top)
         ops.moe_grouped(y, None, 1, self.down, rows, offsets, tiles)
         out = ws.get("moe.out", T, H, ctx.dtype)
-        ops.moe_combine(rows, row_of_pair, weight, self._shared(ctx, first), out)
+        ops.moe_combine(rows, row_of_pair.view(T, s.top), None if s.weight_on_input else weight,
+                        add if add is not None else self._shared(ctx, first), out)
         return out
 
     def _shared(self, ctx, first):
@@ -116,7 +134,7 @@ class RoutedExperts(Part):
         ops.clamped_glu(first, ys, s.shared_limit, s.glu_alpha)
         return self.shared_down(ctx, ys, "moe.shared_out")
 
-    def _forward_tiles(self, ctx, x, first, choice, weight):
+    def _forward_tiles(self, ctx, x, first, choice, weight, add=None):
         s = self.spec
         T, H = x.shape
         ws = ctx.workspace
@@ -130,12 +148,13 @@ class RoutedExperts(Part):
         ops.moe_sort(choice, s.experts, heads[0], heads[1], pair_of_row, row_of_pair, tile_rows=tile,
                      group_of_tile=group_of_tile)
         xs = ws.get("moe.xs", rows_cap, H, ctx.dtype, reserve=0)
-        ops.moe_gather_rows(x, pair_of_row, s.top, xs)
+        ops.moe_gather_rows(x, pair_of_row, s.top, xs, pair_scale=weight if s.weight_on_input else None)
         y = ws.get("moe.y_tiles", rows_cap, s.intermediate_size, ctx.dtype, reserve=0)
-        ops.gemm_tn_tcgen05_grouped(xs, self.gate_up, y, group_of_tile, glu=True, limit=s.limit, alpha=s.glu_alpha,
+        ops.gemm_tn_tcgen05_grouped(xs, self.gate_up, y, group_of_tile, glu=True, limit=self.limit, alpha=s.glu_alpha,
                                     tile_rows=tile)
         rows = ws.get("moe.rows_tiles", rows_cap, H, torch.float32, reserve=0)
         ops.gemm_tn_tcgen05_grouped(y, self.down, rows, group_of_tile, tile_rows=tile)
         out = ws.get("moe.out", T, H, ctx.dtype)
-        ops.moe_combine(rows, row_of_pair, weight, self._shared(ctx, first), out)
+        ops.moe_combine(rows, row_of_pair.view(T, s.top), None if s.weight_on_input else weight,
+                        add if add is not None else self._shared(ctx, first), out)
         return out

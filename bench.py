@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--shape 8b|14b|32b] [--workload decode|mixed]
-    python bench.py --design nekedra|tonanex [--design-size 2048|4096]
+    python bench.py --design nekedra|tonanex|pabalorn [--design-size 2048|4096]
 
 A "step" is one decode step: every request of the batch gets its next token.
 The default run has the sizes of the 8B configuration (36 layers, hidden 4096,
@@ -37,7 +37,9 @@ and decode of four-layer Nekedra stacks (each mixer alone, and mixed) beside the
 Qwen3 decoder at equal width, heads and feed-forward size, with the kernels an
 eager step spends its time in (``run_design``).
 ``--design tonanex`` does the same for Tonanex stacks with a dense feed-forward
-and with routed experts.
+and with routed experts, ``--design pabalorn`` for Pabalorn stacks of attention
+layers, of layers with an attention and a selective scan side by side, and of
+both in turn, beside Qwen3 and the Tonanex stack with routed experts.
 """
 from __future__ import annotations
 
@@ -581,6 +583,27 @@ def tonanex_config(size: dict, kinds) -> dict:
             "layers": [{"type": "attention", "mixer": mixer, "mlp": mlps[k]} for k in kinds]}
 
 
+PABALORN_WINDOW = 1024
+PABALORN_EXPERTS, PABALORN_TOP = 16, 4
+
+
+def pabalorn_config(size: dict, kinds) -> dict:
+    """A Pabalorn configuration whose layers have the sizes of a Qwen3 layer of the same width: heads of 128 for keys
+    and values with half of each head rotated, a window of 1,024 tokens and scores capped at 30; beside the attention
+    of a 'parallel' layer a selective scan of two widths of channels with 16 states each; 16 experts of three quarters
+    of a width of which a token runs 4: three widths of feed-forward rows a token, as in the dense layer."""
+    W, H, G = size["width"], size["heads"], size["kv_heads"]
+    att = {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": PABALORN_WINDOW},
+           "rot": {"base": 10000.0, "dims": 64}}
+    left = dict(att, rot={"base": 10000.0, "dims": 128,
+                          "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
+    right = {"inner": 2 * W, "state": 16, "dt_rank": W // 16, "conv": 4}
+    mixers = {"attention": dict(att, softcap=30.0), "parallel": {"left": left, "right": right}}
+    mlp = {"kind": "moe", "expert": {"ff": 3 * W // 4}, "router": {"experts": PABALORN_EXPERTS, "top": PABALORN_TOP}}
+    return {"architecture": "Pabalorn", "width": W, "vocab": DESIGN_VOCAB, "norm": {"eps": 1e-6},
+            "layers": [{"type": k, "mixer": mixers[k], "mlp": mlp} for k in kinds]}
+
+
 def qwen3_config(size: dict) -> dict:
     return dict(BASE, num_hidden_layers=DESIGN_LAYERS, hidden_size=size["width"], num_attention_heads=size["heads"],
                 num_key_value_heads=size["kv_heads"], intermediate_size=3 * size["width"], vocab_size=DESIGN_VOCAB)
@@ -600,6 +623,11 @@ def run_design(args) -> dict:
     if args.design == "tonanex":
         stacks = {"qwen3": None, "tonanex dense": ["dense"] * DESIGN_LAYERS, "tonanex experts": ["moe"] * DESIGN_LAYERS}
         make = tonanex_config
+    if args.design == "pabalorn":
+        stacks = {"qwen3": None, "tonanex experts": ["moe"] * DESIGN_LAYERS,
+                  "pabalorn attention": ["attention"] * DESIGN_LAYERS, "pabalorn parallel": ["parallel"] * DESIGN_LAYERS,
+                  "pabalorn mixed": ["attention", "parallel"] * (DESIGN_LAYERS // 2)}
+        make = lambda size, kinds: (tonanex_config if kinds[0] == "moe" else pabalorn_config)(size, kinds)
     out = {"metric": args.design + "_beside_qwen3", "layers": DESIGN_LAYERS, "prefill_tokens": PREFILL_TOKENS,
            "decode_batch": batch, "decode_context": context, "dtype": "bf16", "data": "synthetic", "sizes": {}}
     sizes = [args.design_size] if args.design_size else sorted(DESIGN_SIZES)
@@ -645,9 +673,9 @@ def main() -> int:
     ap.add_argument("--only-prefill", action="store_true", help="run just the 2,048-token prefill (for profilers)")
     ap.add_argument("--streaming-kernel", action="store_true",
                     help="steps of up to 8 tokens on the weight-streaming mma.sync kernel instead of the tensor-core one")
-    ap.add_argument("--design", default=None, choices=["nekedra", "tonanex"],
-                    help="instead of the default workload: prefill and decode of Nekedra or Tonanex stacks beside the "
-                         "Qwen3 decoder at equal layer sizes")
+    ap.add_argument("--design", default=None, choices=["nekedra", "tonanex", "pabalorn"],
+                    help="instead of the default workload: prefill and decode of Nekedra, Tonanex or Pabalorn stacks "
+                         "beside the Qwen3 decoder at equal layer sizes")
     ap.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES), help="one width of --design")
     ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
                     help="repeat the block of --steps steps until this much is timed (0: one block, for profilers)")

@@ -29,6 +29,25 @@ bool pdl_enabled();                            // programmatic dependent launch 
 // an earlier kernel wrote or writes anything an earlier kernel reads; what it does before that
 // (barrier set-up, TMEM allocation, loads of weights, which no kernel writes) overlaps the
 // earlier kernel's tail.  pdl_trigger() lets the kernel behind start its own preamble.
+// early = false: the kernel starts only when the one ahead has finished, as a plain launch does.  For a kernel of few
+// long-running blocks: blocks that start while the kernel ahead still drains land on the SMs that happen to be free,
+// many on one, and stay there for their whole walk.
+template <typename... KArgs, typename... Args>
+inline void launch_pdl_if(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = early && pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename... KArgs, typename... Args>
 inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                        Args&&... args) {

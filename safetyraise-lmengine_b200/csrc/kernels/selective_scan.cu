@@ -13,7 +13,9 @@
 //   conv   one thread per (token, channel): reads the step's inputs, and the slot's carried inputs for the first
 //          taps - 1 tokens of an entry
 //   scan   one block per (entry, 16 channels): 8 lanes share a channel's N states and walk the entry's tokens in
-//          order, staged through shared memory in chunks; then the block renews the slot's S and carried inputs.
+//          order, through chunks of 16 tokens fetched one ahead into shared memory; the gate and the write of a
+//          chunk's y are the whole block's work while the next chunk is on its way; then the block renews the
+//          slot's S and carried inputs.
 //          A channel's sums do not depend on what else is in the step or on how the tokens were cut into steps.
 #include <math_constants.h>
 
@@ -52,6 +54,18 @@ __global__ void scan_conv_kernel(const float* __restrict__ xz, long long ld, con
 
 constexpr int kScanLanes = 8, kScanChannels = 16, kScanChunk = 16;
 
+__device__ __forceinline__ void scan_cp_async_4(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src));
+}
+__device__ __forceinline__ void scan_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void scan_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// A chunk of 16 tokens lies in shared memory while the block walks it: B and C of every token, zero behind N up to
+// the lanes' reach; per (token, channel) dt (raw, then its softplus), x, z; and the block's y ahead of the gate.
+// Places behind an entry's last token hold dt = 0, x = 0, B = 0: S <- fma(1, S, 0) leaves every state as it is, so
+// the walk has no branch.  Chunks are fetched one ahead (cp.async) into the other of two buffers.
 template <typename TO, int NPL>
 __global__ void __launch_bounds__(kScanLanes* kScanChannels)
 selective_scan_kernel(const float* __restrict__ x, const float* __restrict__ xz, long long ld_xz,
@@ -59,11 +73,14 @@ selective_scan_kernel(const float* __restrict__ x, const float* __restrict__ xz,
                       const float* __restrict__ dt_bias, const float* __restrict__ A, const float* __restrict__ D,
                       float* __restrict__ state, long long state_stride, const int* __restrict__ cu_q,
                       const int* __restrict__ slots, TO* __restrict__ out, int channels, int N, int taps) {
+  constexpr int NP = NPL * kScanLanes;                      // states a channel's lanes reach, >= N
+  constexpr int GROUP = NPL <= 2 ? 8 : NPL <= 4 ? 4 : 2;    // tokens whose independent work the compiler interleaves
+  constexpr int BC = kScanChunk * 2 * NP, TOK = kScanChunk * kScanChannels * 4, YS = kScanChunk * kScanChannels;
   pdl_wait();
-  pdl_trigger();
-  extern __shared__ float scan_smem[];
-  float* bc_s = scan_smem;                                  // [chunk][2 N]: B, then C
-  float* tok_s = bc_s + kScanChunk * 2 * N;                 // [chunk][channels of the block][3]: dt, x, z
+  extern __shared__ __align__(16) float scan_smem[];
+  float* bc_s = scan_smem;                                  // [2][chunk][2 NP]: B, then C
+  float* tok_s = bc_s + 2 * BC;                             // [2][chunk][channels of the block][4]: dt, x, z, -
+  float* y_s = tok_s + 2 * TOK;                             // [2][chunk][channels of the block]
   const int e = blockIdx.y, c0 = blockIdx.x * kScanChannels;
   const int tid = threadIdx.x, lane = tid % kScanLanes, ch = tid / kScanLanes;
   const int c = c0 + ch;
@@ -78,43 +95,84 @@ selective_scan_kernel(const float* __restrict__ x, const float* __restrict__ xz,
     S[k] = on ? slot[(size_t)c * N + n] : 0.f;
     a[k] = on ? A[(size_t)c * N + n] : 0.f;
   }
-  const float d_c = live ? D[c] : 0.f;
-  for (int base = 0; base < q_len; base += kScanChunk) {
-    const int n_here = min(kScanChunk, q_len - base);
-    __syncthreads();                                        // the chunk before is no longer read
-    for (int idx = tid; idx < n_here * 2 * N; idx += blockDim.x) {
-      const int i = idx / (2 * N), n = idx - i * 2 * N;
-      bc_s[i * 2 * N + n] = dbc[(size_t)(t0 + base + i) * ld_dbc + b_off + n];
+  const int n_chunks = (q_len + kScanChunk - 1) / kScanChunk;
+
+  auto stage = [&](int j) {
+    const int base = j * kScanChunk, n_here = min(kScanChunk, q_len - base);
+    float* bc = bc_s + (j & 1) * BC;
+    float* tk = tok_s + (j & 1) * TOK;
+    for (int idx = tid; idx < kScanChunk * 2 * NP; idx += blockDim.x) {
+      const int i = idx / (2 * NP), r = idx - i * 2 * NP, half = r / NP, n = r - half * NP;
+      if (i < n_here && n < N) scan_cp_async_4(bc + idx, dbc + (size_t)(t0 + base + i) * ld_dbc + b_off + half * N + n);
+      else bc[idx] = 0.f;
     }
+    for (int idx = tid; idx < kScanChunk * kScanChannels; idx += blockDim.x) {
+      const int i = idx / kScanChannels, cc = idx - i * kScanChannels;
+      float* dst = tk + (size_t)idx * 4;
+      if (i < n_here && c0 + cc < channels) {
+        const size_t t = (size_t)(t0 + base + i);
+        scan_cp_async_4(dst, dt_raw + t * channels + c0 + cc);
+        scan_cp_async_4(dst + 1, x + t * channels + c0 + cc);
+        scan_cp_async_4(dst + 2, xz + t * ld_xz + channels + c0 + cc);
+      } else {
+        dst[0] = dst[1] = dst[2] = 0.f;
+      }
+    }
+    scan_cp_async_commit();
+  };
+  // y of chunk j, gated and written: out = (y + D x) * silu(z)
+  auto finish = [&](int j) {
+    const int base = j * kScanChunk, n_here = min(kScanChunk, q_len - base);
+    const float* tk = tok_s + (j & 1) * TOK;
+    const float* ys = y_s + (j & 1) * YS;
     for (int idx = tid; idx < n_here * kScanChannels; idx += blockDim.x) {
       const int i = idx / kScanChannels, cc = idx - i * kScanChannels;
-      const size_t t = (size_t)(t0 + base + i);
-      const bool on = c0 + cc < channels;
-      float* dst = tok_s + (size_t)(i * kScanChannels + cc) * 3;
-      dst[0] = on ? softplus_f(dt_raw[t * channels + c0 + cc] + (dt_bias ? dt_bias[c0 + cc] : 0.f)) : 0.f;
-      dst[1] = on ? x[t * channels + c0 + cc] : 0.f;
-      dst[2] = on ? xz[t * ld_xz + channels + c0 + cc] : 0.f;
-    }
-    __syncthreads();
-    for (int i = 0; i < n_here; ++i) {
-      const float* tk = tok_s + (size_t)(i * kScanChannels + ch) * 3;
-      const float dt = tk[0], xv = tk[1], z = tk[2];
-      const float dtx = dt * xv;
-      const float* Bt = bc_s + i * 2 * N;
-      float y = 0.f;
-#pragma unroll
-      for (int k = 0; k < NPL; ++k) {
-        const int n = lane + k * kScanLanes;
-        if (n < N) {
-          S[k] = fmaf(expf(dt * a[k]), S[k], dtx * Bt[n]);
-          y = fmaf(S[k], Bt[N + n], y);
-        }
+      if (c0 + cc < channels) {
+        const float xv = tk[idx * 4 + 1], z = tk[idx * 4 + 2];
+        out[(size_t)(t0 + base + i) * channels + c0 + cc] = from_float<TO>((ys[idx] + D[c0 + cc] * xv) * silu_f(z));
       }
+    }
+  };
+
+  if (n_chunks > 0) stage(0);
+  for (int j = 0; j < n_chunks; ++j) {
+    const int base = j * kScanChunk, n_here = min(kScanChunk, q_len - base);
+    float* bc = bc_s + (j & 1) * BC;
+    float* tk = tok_s + (j & 1) * TOK;
+    float* ys = y_s + (j & 1) * YS;
+    scan_cp_async_wait<0>();
+    __syncthreads();                                        // chunk j has landed; the walk over chunk j - 1 is over
+    for (int idx = tid; idx < kScanChunk * kScanChannels; idx += blockDim.x) {
+      const int i = idx / kScanChannels, cc = idx - i * kScanChannels;
+      if (i < n_here && c0 + cc < channels) tk[idx * 4] = softplus_f(tk[idx * 4] + (dt_bias ? dt_bias[c0 + cc] : 0.f));
+    }
+    if (j > 0) finish(j - 1);
+    __syncthreads();                                        // the other buffer is free again
+    if (j + 1 < n_chunks) stage(j + 1);
+#pragma unroll 1
+    for (int i0 = 0; i0 < n_here; i0 += GROUP) {
 #pragma unroll
-      for (int o = kScanLanes / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-      if (lane == 0 && live) out[(size_t)(t0 + base + i) * channels + c] = from_float<TO>((y + d_c * xv) * silu_f(z));
+      for (int u = 0; u < GROUP; ++u) {
+        const int i = i0 + u;
+        const float4 v = *reinterpret_cast<const float4*>(tk + (size_t)(i * kScanChannels + ch) * 4);
+        const float dt = v.x, dtx = v.x * v.y;
+        const float* Bt = bc + i * 2 * NP;
+        float y = 0.f;
+#pragma unroll
+        for (int k = 0; k < NPL; ++k) {
+          const int n = lane + k * kScanLanes;
+          S[k] = fmaf(expf(dt * a[k]), S[k], dtx * Bt[n]);
+          y = fmaf(S[k], Bt[NP + n], y);
+        }
+#pragma unroll
+        for (int o = kScanLanes / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+        if (lane == 0) ys[i * kScanChannels + ch] = y;
+      }
     }
   }
+  pdl_trigger();             // a long walk: the kernel behind would only sit on the SMs meanwhile
+  __syncthreads();
+  if (n_chunks > 0) finish(n_chunks - 1);
 #pragma unroll
   for (int k = 0; k < NPL; ++k) {
     const int n = lane + k * kScanLanes;
@@ -182,22 +240,26 @@ extern "C" int srlm_scan_conv(const float* xz, long long ld, const float* conv_w
 
 // x float32 [T, channels] (behind the convolution); xz float32 [T, ld_xz >= 2 channels]: the convolution's inputs, then z;
 // dbc float32 [T, ld_dbc]: B in columns [b_off, b_off + N), C in the N columns behind them; dt_raw float32
-// [T, channels]; dt_bias, D float32 [channels]; A float32 [channels, N]; out [T, channels] in out_dtype.
+// [T, channels]; dt_bias, D float32 [channels]; A float32 [channels, N]; out [T, channels] in out_dtype.  max_q_len: the
+// most tokens an entry brings (an upper bound will do).
 extern "C" int srlm_selective_scan(const float* x, const float* xz, long long ld_xz, const float* dbc, long long ld_dbc,
                                    int b_off, const float* dt_raw, const float* dt_bias, const float* A, const float* D,
                                    float* state, long long state_stride, const int* cu_q, const int* slots, void* out,
-                                   int out_dtype, int n_entries, int channels, int N, int taps, cudaStream_t stream) {
+                                   int out_dtype, int n_entries, int max_q_len, int channels, int N, int taps,
+                                   cudaStream_t stream) {
   if (n_entries <= 0) return ST_OK;
   if (channels <= 0 || N <= 0 || N > 16 * kScanLanes || taps <= 0 || ld_xz < 2ll * channels || b_off < 0 ||
       ld_dbc < b_off + 2ll * N || state_stride < (long long)channels * (N + taps - 1) || n_entries > 65535)
     return refuse(ST_BAD_SIZE, "selective_scan: channels=%d N=%d (at most %d) taps=%d ld_xz=%lld ld_dbc=%lld b_off=%d "
                   "state_stride=%lld", channels, N, 16 * kScanLanes, taps, ld_xz, ld_dbc, b_off, state_stride);
   const dim3 grid((channels + kScanChannels - 1) / kScanChannels, n_entries);
-  const size_t smem = (size_t)kScanChunk * (2 * N + 3 * kScanChannels) * sizeof(float);
   int npl = 1;
   while (npl * kScanLanes < N) npl <<= 1;
+  const bool early = max_q_len <= 4 * kScanChunk;      // a long walk starts on an empty GPU, its blocks spread evenly
+  // two buffers of a chunk: B | C up to the lanes' reach, four words per (token, channel), the block's y
+  const size_t smem = (size_t)2 * kScanChunk * (2 * npl * kScanLanes + 5 * kScanChannels) * sizeof(float);
 #define SRLM_SCAN(TO, NPL)                                                                                              \
-  launch_pdl(selective_scan_kernel<TO, NPL>, grid, dim3(kScanLanes * kScanChannels), smem, stream, x, xz, ld_xz, dbc, ld_dbc, \
+  launch_pdl_if(early, selective_scan_kernel<TO, NPL>, grid, dim3(kScanLanes * kScanChannels), smem, stream, x, xz, ld_xz, dbc, ld_dbc, \
              b_off, dt_raw, dt_bias, A, D, state, state_stride, cu_q, slots, (TO*)out, channels, N, taps)
 #define SRLM_SCAN_N(TO)                                   \
   switch (npl) {                                          \

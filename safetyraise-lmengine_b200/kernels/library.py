@@ -1075,7 +1075,7 @@ class KernelLibrary:
         self._check(self.lib.srlm_selective_scan(
             _ptr(x), _ptr(xz), C.c_longlong(xz.stride(0)), _ptr(dbc), C.c_longlong(dbc.stride(0)), C.c_int(b_off),
             _ptr(dt_raw), _ptr(dt_bias), _ptr(A), _ptr(D), _ptr(state), C.c_longlong(state.stride(0)), _ptr(ctx.cu_q),
-            _ptr(ctx.slots), _ptr(out), dtype_code(out.dtype), C.c_int(ctx.n_entries), C.c_int(channels), C.c_int(N),
+            _ptr(ctx.slots), _ptr(out), dtype_code(out.dtype), C.c_int(ctx.n_entries), C.c_int(ctx.max_q_len), C.c_int(channels), C.c_int(N),
             C.c_int(taps), _stream()), "selective_scan")
 
     def paired_rmsnorm_mean(self, a, wa, b, wb, eps, out):

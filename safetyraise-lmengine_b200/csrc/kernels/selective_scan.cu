@@ -10,10 +10,11 @@
 // every channel's convolution.  Everything here is float32 arithmetic; only `out` (the input of the output product)
 // and the optional second copy of x (the input of the B / C / dt product) are written in the activation dtype.
 //
-//   conv   one thread per (token, channel): reads the step's inputs, and the slot's carried inputs for the first
-//          taps - 1 tokens of an entry
+//   conv   one thread per (token, four neighbouring channels; one where rows do not allow 16-byte accesses): reads
+//          the step's inputs, and the slot's carried inputs for the first taps - 1 tokens of an entry
 //   scan   one block per (entry, 16 channels): 8 lanes share a channel's N states and walk the entry's tokens in
-//          order, through chunks of 16 tokens fetched one ahead into shared memory; the gate and the write of a
+//          order, through chunks of 16 tokens fetched one ahead into shared memory; the lanes' partial sums of 8
+//          tokens are added in one exchange of 7 shuffles; the gate and the write of a
 //          chunk's y are the whole block's work while the next chunk is on its way; then the block renews the
 //          slot's S and carried inputs.
 //          A channel's sums do not depend on what else is in the step or on how the tokens were cut into steps.
@@ -27,7 +28,7 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); 
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 // state of a slot: [channels * N] S, then [channels * (taps - 1)] carried inputs, oldest first
-template <typename TL>
+template <typename TL, int V>
 __global__ void scan_conv_kernel(const float* __restrict__ xz, long long ld, const float* __restrict__ conv_w,
                                  const float* __restrict__ conv_b, const float* __restrict__ state, long long state_stride,
                                  const int* __restrict__ entry_of_token, const int* __restrict__ cu_q,
@@ -35,21 +36,54 @@ __global__ void scan_conv_kernel(const float* __restrict__ xz, long long ld, con
                                  int T, int channels, int N, int taps) {
   pdl_wait();
   pdl_trigger();
+  const int per_token = channels / V;                      // V neighbouring channels a thread (V divides channels)
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (long long)T * channels) return;
-  const int t = (int)(idx / channels), c = (int)(idx - (long long)t * channels);
+  if (idx >= (long long)T * per_token) return;
+  const int t = (int)(idx / per_token), c = (int)(idx - (long long)t * per_token) * V;
   const int e = entry_of_token[t];
   const int i = t - cu_q[e];                               // the token's place in its entry
   const float* carry = state + (size_t)slots[e] * state_stride + (size_t)channels * N + (size_t)c * (taps - 1);
-  float acc = conv_b ? conv_b[c] : 0.f;
+  float acc[V], v[V];
+#pragma unroll
+  for (int u = 0; u < V; ++u) acc[u] = conv_b ? conv_b[c + u] : 0.f;
   for (int j = 0; j < taps; ++j) {
     const int back = taps - 1 - j;                         // tap j weighs the input `back` tokens ago
-    const float v = back <= i ? xz[(size_t)(t - back) * ld + c] : carry[taps - 1 + i - back];
-    acc = fmaf(conv_w[(size_t)c * taps + j], v, acc);
+    if (back <= i) {
+      const float* src = xz + (size_t)(t - back) * ld + c;
+      if constexpr (V == 4) {
+        const float4 f = *reinterpret_cast<const float4*>(src);
+        v[0] = f.x, v[1] = f.y, v[2] = f.z, v[3] = f.w;
+      } else {
+#pragma unroll
+        for (int u = 0; u < V; ++u) v[u] = src[u];
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < V; ++u) v[u] = carry[(size_t)u * (taps - 1) + taps - 1 + i - back];
+    }
+#pragma unroll
+    for (int u = 0; u < V; ++u) acc[u] = fmaf(conv_w[(size_t)(c + u) * taps + j], v[u], acc[u]);
   }
-  const float y = silu_f(acc);
-  x_out[idx] = y;
-  if (x_low) x_low[idx] = from_float<TL>(y);
+#pragma unroll
+  for (int u = 0; u < V; ++u) acc[u] = silu_f(acc[u]);
+  const size_t at = (size_t)t * channels + c;
+  if constexpr (V == 4) {
+    *reinterpret_cast<float4*>(x_out + at) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  } else {
+#pragma unroll
+    for (int u = 0; u < V; ++u) x_out[at + u] = acc[u];
+  }
+  if (x_low) {
+    if constexpr (V == 4 && sizeof(TL) == 2) {               // four 16-bit values in one 8-byte store
+      TL low[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) low[u] = from_float<TL>(acc[u]);
+      *reinterpret_cast<uint2*>(x_low + at) = *reinterpret_cast<const uint2*>(low);
+    } else {
+#pragma unroll
+      for (int u = 0; u < V; ++u) x_low[at + u] = from_float<TL>(acc[u]);
+    }
+  }
 }
 
 constexpr int kScanLanes = 8, kScanChannels = 16, kScanChunk = 16;
@@ -61,6 +95,25 @@ __device__ __forceinline__ void scan_cp_async_4(float* dst, const float* src) {
 __device__ __forceinline__ void scan_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void scan_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// n neighbouring floats of shared memory (n a power of two; the address a multiple of min(n, 4) floats)
+template <int NPL>
+__device__ __forceinline__ void scan_load_row(const float* src, float (&dst)[NPL]) {
+  if constexpr (NPL == 1) {
+    dst[0] = src[0];
+  } else if constexpr (NPL == 2) {
+    const float2 f = *reinterpret_cast<const float2*>(src);
+    dst[0] = f.x, dst[1] = f.y;
+  } else {
+#pragma unroll
+    for (int k = 0; k < NPL; k += 4) {
+      const float4 f = *reinterpret_cast<const float4*>(src + k);
+      dst[k] = f.x, dst[k + 1] = f.y, dst[k + 2] = f.z, dst[k + 3] = f.w;
+    }
+  }
+}
 
 // A chunk of 16 tokens lies in shared memory while the block walks it: B and C of every token, zero behind N up to
 // the lanes' reach; per (token, channel) dt (raw, then its softplus), x, z; and the block's y ahead of the gate.
@@ -87,13 +140,13 @@ selective_scan_kernel(const float* __restrict__ x, const float* __restrict__ xz,
   const bool live = c < channels;
   const int t0 = cu_q[e], q_len = cu_q[e + 1] - t0;
   float* slot = state + (size_t)slots[e] * state_stride;
-  float S[NPL], a[NPL];
+  float S[NPL], a[NPL];                                     // a lane's states are neighbours: n = lane * NPL + k
 #pragma unroll
   for (int k = 0; k < NPL; ++k) {
-    const int n = lane + k * kScanLanes;
+    const int n = lane * NPL + k;
     const bool on = live && n < N;
     S[k] = on ? slot[(size_t)c * N + n] : 0.f;
-    a[k] = on ? A[(size_t)c * N + n] : 0.f;
+    a[k] = on ? A[(size_t)c * N + n] * kLog2e : 0.f;        // exp(dt A) = 2^(dt A log2 e)
   }
   const int n_chunks = (q_len + kScanChunk - 1) / kScanChunk;
 
@@ -151,23 +204,44 @@ selective_scan_kernel(const float* __restrict__ x, const float* __restrict__ xz,
     if (j + 1 < n_chunks) stage(j + 1);
 #pragma unroll 1
     for (int i0 = 0; i0 < n_here; i0 += GROUP) {
+      float y[GROUP];
 #pragma unroll
       for (int u = 0; u < GROUP; ++u) {
         const int i = i0 + u;
         const float4 v = *reinterpret_cast<const float4*>(tk + (size_t)(i * kScanChannels + ch) * 4);
         const float dt = v.x, dtx = v.x * v.y;
-        const float* Bt = bc + i * 2 * NP;
-        float y = 0.f;
+        float Bv[NPL], Cv[NPL];
+        scan_load_row<NPL>(bc + i * 2 * NP + lane * NPL, Bv);
+        scan_load_row<NPL>(bc + i * 2 * NP + NP + lane * NPL, Cv);
+        y[u] = 0.f;
 #pragma unroll
         for (int k = 0; k < NPL; ++k) {
-          const int n = lane + k * kScanLanes;
-          S[k] = fmaf(expf(dt * a[k]), S[k], dtx * Bt[n]);
-          y = fmaf(S[k], Bt[NP + n], y);
+          S[k] = fmaf(exp2f(dt * a[k]), S[k], dtx * Bv[k]);
+          y[u] = fmaf(S[k], Cv[k], y[u]);
         }
-#pragma unroll
-        for (int o = kScanLanes / 2; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-        if (lane == 0) ys[i * kScanChannels + ch] = y;
       }
+      // the lanes' partial sums of GROUP tokens, added across the 8 lanes: each round a lane hands half of what it
+      // holds to its partner and keeps the other half, so 8 tokens cost 4 + 2 + 1 exchanges, and lane l ends with
+      // token l's sum; a group of fewer tokens ends with plain rounds (both partners then hold the sum)
+      int held = GROUP, tok = 0;
+#pragma unroll
+      for (int o = kScanLanes / 2; o > 0; o >>= 1) {
+        if (held > 1) {
+          const int h = held / 2;
+          const bool upper = (lane & o) != 0;
+#pragma unroll
+          for (int u = 0; u < GROUP / 2; ++u)
+            if (u < h) {
+              const float send = upper ? y[u] : y[u + h], keep = upper ? y[u + h] : y[u];
+              y[u] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+            }
+          tok += upper ? h : 0;
+          held = h;
+        } else {
+          y[0] += __shfl_xor_sync(0xffffffffu, y[0], o);
+        }
+      }
+      if ((lane & (kScanLanes / GROUP - 1)) == 0) ys[(i0 + tok) * kScanChannels + ch] = y[0];
     }
   }
   pdl_trigger();             // a long walk: the kernel behind would only sit on the SMs meanwhile
@@ -175,7 +249,7 @@ selective_scan_kernel(const float* __restrict__ x, const float* __restrict__ xz,
   if (n_chunks > 0) finish(n_chunks - 1);
 #pragma unroll
   for (int k = 0; k < NPL; ++k) {
-    const int n = lane + k * kScanLanes;
+    const int n = lane * NPL + k;
     if (live && n < N) slot[(size_t)c * N + n] = S[k];
   }
   // the carried inputs: the last taps - 1 inputs of the channel, of this step or, for a short one, shifted up
@@ -189,24 +263,60 @@ selective_scan_kernel(const float* __restrict__ x, const float* __restrict__ xz,
 }
 
 // out = (wa * a / sqrt(mean(a^2) + eps) + wb * b / sqrt(mean(b^2) + eps)) / 2: two sublayers that read the same input,
-// each result normed with its own weight, averaged.  One block per token; sums in float32 in an order fixed by the width.
-template <typename TI, typename TO>
+// each result normed with its own weight, averaged.  One block per token; sums in float32 in an order fixed by the width
+// and the block's size.  V elements a thread and access (V = 4 where rows and pointers allow 16 bytes of float32); a
+// thread keeps its first PER accesses of a and b in registers for the second pass and reads the rest again.
+template <typename TI, typename TO, int V, int PER>
 __global__ void paired_rmsnorm_mean_kernel(const TI* __restrict__ a, const float* __restrict__ wa, const TI* __restrict__ b,
                                            const float* __restrict__ wb, float eps, TO* __restrict__ out, int H) {
   pdl_wait();
   pdl_trigger();
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * H;
+  const int step = blockDim.x * V;
+  float ua[PER][V], ub[PER][V];
   float sa = 0.f, sb = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float u = to_float(a[base + i]), v = to_float(b[base + i]);
-    sa += u * u;
-    sb += v * v;
+  auto fetch = [&](int i, float (&u)[V], float (&v)[V]) {
+    if constexpr (V == 4 && sizeof(TI) == 4) {
+      const float4 f = *reinterpret_cast<const float4*>(a + base + i), g = *reinterpret_cast<const float4*>(b + base + i);
+      u[0] = f.x, u[1] = f.y, u[2] = f.z, u[3] = f.w;
+      v[0] = g.x, v[1] = g.y, v[2] = g.z, v[3] = g.w;
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; ++k) u[k] = to_float(a[base + i + k]), v[k] = to_float(b[base + i + k]);
+    }
+  };
+  int r = 0;
+  for (int i = threadIdx.x * V; i < H; i += step, ++r) {
+    float u[V], v[V];
+    fetch(i, u, v);
+#pragma unroll
+    for (int k = 0; k < V; ++k) sa = fmaf(u[k], u[k], sa), sb = fmaf(v[k], v[k], sb);
+#pragma unroll
+    for (int p = 0; p < PER; ++p)
+      if (p == r) {
+#pragma unroll
+        for (int k = 0; k < V; ++k) ua[p][k] = u[k], ub[p][k] = v[k];
+      }
   }
   const float ia = 1.0f / sqrtf(block_sum(sa, scratch) / (float)H + eps);
   const float ib = 1.0f / sqrtf(block_sum(sb, scratch) / (float)H + eps);
-  for (int i = threadIdx.x; i < H; i += blockDim.x)
-    out[base + i] = from_float<TO>(0.5f * (to_float(a[base + i]) * ia * wa[i] + to_float(b[base + i]) * ib * wb[i]));
+  r = 0;
+  for (int i = threadIdx.x * V; i < H; i += step, ++r) {
+    float u[V], v[V];
+    bool kept = false;
+#pragma unroll
+    for (int p = 0; p < PER; ++p)
+      if (p == r) {
+        kept = true;
+#pragma unroll
+        for (int k = 0; k < V; ++k) u[k] = ua[p][k], v[k] = ub[p][k];
+      }
+    if (!kept) fetch(i, u, v);
+#pragma unroll
+    for (int k = 0; k < V; ++k)
+      out[base + i + k] = from_float<TO>(0.5f * (u[k] * ia * wa[i + k] + v[k] * ib * wb[i + k]));
+  }
 }
 
 }  // namespace srlm
@@ -225,16 +335,23 @@ extern "C" int srlm_scan_conv(const float* xz, long long ld, const float* conv_w
   if (channels <= 0 || N <= 0 || taps <= 0 || ld < channels || state_stride < (long long)channels * (N + taps - 1))
     return refuse(ST_BAD_SIZE, "scan_conv: channels=%d N=%d taps=%d ld=%lld state_stride=%lld", channels, N, taps, ld,
                   state_stride);
-  const long long total = (long long)T * channels;
+  // four neighbouring channels a thread where rows and pointers allow 16-byte accesses (the sums are the same)
+  const bool wide = channels % 4 == 0 && ld % 4 == 0 && ((uintptr_t)xz | (uintptr_t)x_out | (uintptr_t)x_low) % 16 == 0;
+  const long long total = (long long)T * (wide ? channels / 4 : channels);
   const dim3 grid((unsigned)((total + 255) / 256));
-  if (!x_low)
-    launch_pdl(scan_conv_kernel<float>, grid, dim3(256), 0, stream, xz, ld, conv_w, conv_b, state, state_stride,
-               entry_of_token, cu_q, slots, x_out, (float*)nullptr, T, channels, N, taps);
-  else if (low_dtype == DT_BF16)
-    launch_pdl(scan_conv_kernel<bf16>, grid, dim3(256), 0, stream, xz, ld, conv_w, conv_b, state, state_stride,
-               entry_of_token, cu_q, slots, x_out, (bf16*)x_low, T, channels, N, taps);
-  else
+#define SRLM_CONV(TL, V, LOW)                                                                                          \
+  launch_pdl(scan_conv_kernel<TL, V>, grid, dim3(256), 0, stream, xz, ld, conv_w, conv_b, state, state_stride,        \
+             entry_of_token, cu_q, slots, x_out, LOW, T, channels, N, taps)
+  if (!x_low) {
+    if (wide) SRLM_CONV(float, 4, (float*)nullptr);
+    else SRLM_CONV(float, 1, (float*)nullptr);
+  } else if (low_dtype == DT_BF16) {
+    if (wide) SRLM_CONV(bf16, 4, (bf16*)x_low);
+    else SRLM_CONV(bf16, 1, (bf16*)x_low);
+  } else {
     return refuse(ST_BAD_DTYPE, "scan_conv: the second copy of x is bfloat16 (dtype %d)", low_dtype);
+  }
+#undef SRLM_CONV
   return launched();
 }
 
@@ -282,11 +399,17 @@ extern "C" int srlm_paired_rmsnorm_mean(const void* a, const float* wa, const vo
                                         int in_dtype, int out_dtype, int T, int H, cudaStream_t stream) {
   if (T <= 0) return ST_OK;
   if (H <= 0 || !(eps > 0.f) || !wa || !wb) return refuse(ST_BAD_SIZE, "paired_rmsnorm_mean: H=%d eps=%g", H, (double)eps);
+  const bool wide = H % 4 == 0 && ((uintptr_t)a | (uintptr_t)b) % 16 == 0;
+  const int v = wide ? 4 : 1;
   int block = 64;
-  while (block < 1024 && block * 4 < H) block <<= 1;
-#define SRLM_PAIRED(TI, TO)                                                                                    \
-  launch_pdl(paired_rmsnorm_mean_kernel<TI, TO>, dim3(T), dim3(block), 0, stream, (const TI*)a, wa, (const TI*)b, wb, eps, \
-             (TO*)out, H)
+  while (block < 1024 && block * 2 * v < H) block <<= 1;      // two accesses a thread, kept in registers between the passes
+#define SRLM_PAIRED(TI, TO)                                                                                              \
+  do {                                                                                                                   \
+    if (wide) launch_pdl(paired_rmsnorm_mean_kernel<TI, TO, 4, 2>, dim3(T), dim3(block), 0, stream, (const TI*)a, wa,    \
+                         (const TI*)b, wb, eps, (TO*)out, H);                                                            \
+    else launch_pdl(paired_rmsnorm_mean_kernel<TI, TO, 1, 2>, dim3(T), dim3(block), 0, stream, (const TI*)a, wa,         \
+                    (const TI*)b, wb, eps, (TO*)out, H);                                                                 \
+  } while (0)
   if (in_dtype == DT_F32 && out_dtype == DT_F32) SRLM_PAIRED(float, float);
   else if (in_dtype == DT_F32 && out_dtype == DT_BF16) SRLM_PAIRED(float, bf16);
   else if (in_dtype == DT_BF16 && out_dtype == DT_BF16) SRLM_PAIRED(bf16, bf16);

@@ -238,11 +238,14 @@ __device__ __forceinline__ void modify_row(Row& r, float factor, float weight_q,
   part(r.d, 96);
 }
 // S <- c1 * tanh(S * c2): the cap of the scaled scores, with c2 = factor * scale / cap and c1 = cap / scale, so that the
-// row, once multiplied by the score scale like a plain row, holds the capped score.  tanh.approx: 2^-11 relative.
+// row, once multiplied by the score scale like a plain row, holds the capped score.  tanh(x) = (1 - t) / (1 + t) with
+// t = 2^(-2 |x| log2 e): two transcendentals (ex2, rcp) and an absolute error of a few 2^-24, where tanh.approx has a
+// relative error of 2^-11, which at a score near the cap is cap * 2^-11.
 __device__ __forceinline__ float tanh_fast(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
+  float t, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fabsf(x) * -2.8853900817779268f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + t));
+  return copysignf((1.f - t) * r, x);
 }
 __device__ __forceinline__ void cap_row(Row& r, float c1, float c2) {
   auto part = [&](uint32_t (&v)[32]) {

@@ -86,6 +86,76 @@ __global__ void scan_conv_kernel(const float* __restrict__ xz, long long ld, con
   }
 }
 
+// The same convolution for rows that allow 16-byte accesses and 2 to 4 taps: a thread owns four neighbouring channels
+// over a run of tokens, holds their weights and the rows of the last TAPS - 1 tokens in registers, and reads every
+// row once.  The sums are formed in the order of the kernel above (bias, then the taps from the oldest on).
+template <typename TL, int TAPS>
+__global__ void scan_conv_rows_kernel(const float* __restrict__ xz, long long ld, const float* __restrict__ conv_w,
+                                      const float* __restrict__ conv_b, const float* __restrict__ state,
+                                      long long state_stride, const int* __restrict__ entry_of_token,
+                                      const int* __restrict__ cu_q, const int* __restrict__ slots,
+                                      float* __restrict__ x_out, TL* __restrict__ x_low, int T, int channels, int N,
+                                      int run) {
+  pdl_wait();
+  pdl_trigger();
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (c >= channels) return;
+  const int t_begin = blockIdx.y * run, t_end = min(T, t_begin + run);
+  float w[4][TAPS], bias[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    bias[u] = conv_b ? conv_b[c + u] : 0.f;
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) w[u][j] = conv_w[(size_t)(c + u) * TAPS + j];
+  }
+  float4 prev[TAPS - 1];                                   // prev[k]: the row of token t - (TAPS - 1) + k
+#pragma unroll
+  for (int k = 0; k < TAPS - 1; ++k) {
+    const int row = t_begin - (TAPS - 1) + k;
+    prev[k] = row >= 0 ? *reinterpret_cast<const float4*>(xz + (size_t)row * ld + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll 4
+  for (int t = t_begin; t < t_end; ++t) {
+    const int e = entry_of_token[t];
+    const int i = t - cu_q[e];                             // the token's place in its entry
+    const float4 cur = *reinterpret_cast<const float4*>(xz + (size_t)t * ld + c);
+    float acc[4] = {bias[0], bias[1], bias[2], bias[3]};
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) {
+      const int back = TAPS - 1 - j;                       // tap j weighs the input `back` tokens ago
+      float v[4];
+      if (back <= i) {                                     // a row of this step (and of this entry)
+        const float4 f = back == 0 ? cur : prev[j];
+        v[0] = f.x, v[1] = f.y, v[2] = f.z, v[3] = f.w;
+      } else {                                             // ahead of the portion: the slot's carried inputs
+        const float* carry = state + (size_t)slots[e] * state_stride + (size_t)channels * N + (size_t)c * (TAPS - 1);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = carry[(size_t)u * (TAPS - 1) + TAPS - 1 + i - back];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) acc[u] = fmaf(w[u][j], v[u], acc[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u] = silu_f(acc[u]);
+    const size_t at = (size_t)t * channels + c;
+    *reinterpret_cast<float4*>(x_out + at) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    if (x_low) {
+      if constexpr (sizeof(TL) == 2) {
+        TL low[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) low[u] = from_float<TL>(acc[u]);
+        *reinterpret_cast<uint2*>(x_low + at) = *reinterpret_cast<const uint2*>(low);
+      } else {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) x_low[at + u] = from_float<TL>(acc[u]);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k + 1 < TAPS - 1; ++k) prev[k] = prev[k + 1];
+    prev[TAPS - 2] = cur;
+  }
+}
+
 constexpr int kScanLanes = 8, kScanChannels = 16, kScanChunk = 16;
 
 __device__ __forceinline__ void scan_cp_async_4(float* dst, const float* src) {
@@ -97,6 +167,13 @@ template <int N>
 __device__ __forceinline__ void scan_cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 constexpr float kLog2e = 1.4426950408889634f;
+
+// 2^x for x <= 0 (a decay): the hardware's approximation, 2 ulp, zero below 2^-126
+__device__ __forceinline__ float scan_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 // n neighbouring floats of shared memory (n a power of two; the address a multiple of min(n, 4) floats)
 template <int NPL>
@@ -216,7 +293,7 @@ selective_scan_kernel(const float* __restrict__ x, const float* __restrict__ xz,
         y[u] = 0.f;
 #pragma unroll
         for (int k = 0; k < NPL; ++k) {
-          S[k] = fmaf(exp2f(dt * a[k]), S[k], dtx * Bv[k]);
+          S[k] = fmaf(scan_exp2(dt * a[k]), S[k], dtx * Bv[k]);
           y[u] = fmaf(S[k], Cv[k], y[u]);
         }
       }
@@ -339,6 +416,25 @@ extern "C" int srlm_scan_conv(const float* xz, long long ld, const float* conv_w
   const bool wide = channels % 4 == 0 && ld % 4 == 0 && ((uintptr_t)xz | (uintptr_t)x_out | (uintptr_t)x_low) % 16 == 0;
   const long long total = (long long)T * (wide ? channels / 4 : channels);
   const dim3 grid((unsigned)((total + 255) / 256));
+  if (wide && taps >= 2 && taps <= 4) {                      // rows read once, weights in registers
+    const int run = T >= 512 ? 16 : 4;
+    const dim3 rows_grid((channels / 4 + 127) / 128, (T + run - 1) / run);
+#define SRLM_CONV_ROWS(TL, TAPS, LOW)                                                                                   \
+  launch_pdl(scan_conv_rows_kernel<TL, TAPS>, rows_grid, dim3(128), 0, stream, xz, ld, conv_w, conv_b, state,          \
+             state_stride, entry_of_token, cu_q, slots, x_out, LOW, T, channels, N, run)
+#define SRLM_CONV_TAPS(TL, LOW)                                  \
+  switch (taps) {                                                \
+    case 2: SRLM_CONV_ROWS(TL, 2, LOW); break;                   \
+    case 3: SRLM_CONV_ROWS(TL, 3, LOW); break;                   \
+    default: SRLM_CONV_ROWS(TL, 4, LOW); break;                  \
+  }
+    if (!x_low) { SRLM_CONV_TAPS(float, (float*)nullptr) }
+    else if (low_dtype == DT_BF16) { SRLM_CONV_TAPS(bf16, (bf16*)x_low) }
+    else return refuse(ST_BAD_DTYPE, "scan_conv: the second copy of x is bfloat16 (dtype %d)", low_dtype);
+#undef SRLM_CONV_TAPS
+#undef SRLM_CONV_ROWS
+    return launched();
+  }
 #define SRLM_CONV(TL, V, LOW)                                                                                          \
   launch_pdl(scan_conv_kernel<TL, V>, grid, dim3(256), 0, stream, xz, ld, conv_w, conv_b, state, state_stride,        \
              entry_of_token, cu_q, slots, x_out, LOW, T, channels, N, taps)

@@ -12,13 +12,15 @@
 //
 //   conv   one thread per (token, four neighbouring channels; one where rows do not allow 16-byte accesses): reads
 //          the step's inputs, and the slot's carried inputs for the first taps - 1 tokens of an entry
-//   scan   one block per (entry, 16 channels): 8 lanes share a channel's N states and walk the entry's tokens in
-//          order, through chunks of 16 tokens fetched one ahead into shared memory; the lanes' partial sums of 8
-//          tokens are added in one exchange of 7 shuffles; the gate and the write of a
-//          chunk's y are the whole block's work while the next chunk is on its way; then the block renews the
-//          slot's S and carried inputs.
+//   scan   one block per (entry, 16 channels): four warps walk the entry's tokens in order, 8 lanes sharing a channel's
+//          N states, through chunks of 16 tokens in shared memory; the lanes' partial sums of 8 tokens are added in
+//          one exchange of 7 shuffles.  Four more warps fetch the chunks several ahead (cp.async), form the step
+//          sizes, and gate and write a finished chunk's y as a block; at the end the walkers renew the slot's S and
+//          carried inputs.
 //          A channel's sums do not depend on what else is in the step or on how the tokens were cut into steps.
 #include <math_constants.h>
+
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -195,9 +197,20 @@ __device__ __forceinline__ void scan_load_row(const float* src, float (&dst)[NPL
 // A chunk of 16 tokens lies in shared memory while the block walks it: B and C of every token, zero behind N up to
 // the lanes' reach; per (token, channel) dt (raw, then its softplus), x, z; and the block's y ahead of the gate.
 // Places behind an entry's last token hold dt = 0, x = 0, B = 0: S <- fma(1, S, 0) leaves every state as it is, so
-// the walk has no branch.  Chunks are fetched one ahead (cp.async) into the other of two buffers.
+// the walk has no branch.
+//
+// The block's first four warps walk; its other four fetch, prepare and finish.  While the walkers are on chunk j the
+// helpers wait for chunk j + 1 (cp.async), turn its raw step sizes into softplus(dt + bias), gate and write the y of
+// chunk j - 1, and issue the fetch of chunk j + K - 1 into the buffer chunk j - 1 has left: K buffers of operands
+// (a fetch has K - 2 walks of a chunk to arrive: a chunk's walk is shorter than a trip to DRAM), two of y, one
+// barrier a chunk.  Every round commits one group of copies, an empty one behind the entry's end, so that "all but
+// the last K - 3 groups" always names chunk j + 1.  A helper prepares and finishes exactly the (token, channel)
+// places it fetched, so only the barrier orders helpers and walkers.
+constexpr int kScanWalkers = kScanLanes * kScanChannels, kScanThreads = 2 * kScanWalkers;
+constexpr int scan_buffers(int npl) { return npl <= 2 ? 6 : npl <= 4 ? 5 : 4; }
+
 template <typename TO, int NPL>
-__global__ void __launch_bounds__(kScanLanes* kScanChannels)
+__global__ void __launch_bounds__(kScanThreads)
 selective_scan_kernel(const float* __restrict__ x, const float* __restrict__ xz, long long ld_xz,
                       const float* __restrict__ dbc, long long ld_dbc, int b_off, const float* __restrict__ dt_raw,
                       const float* __restrict__ dt_bias, const float* __restrict__ A, const float* __restrict__ D,
@@ -206,37 +219,37 @@ selective_scan_kernel(const float* __restrict__ x, const float* __restrict__ xz,
   constexpr int NP = NPL * kScanLanes;                      // states a channel's lanes reach, >= N
   constexpr int GROUP = NPL <= 2 ? 8 : NPL <= 4 ? 4 : 2;    // tokens whose independent work the compiler interleaves
   constexpr int BC = kScanChunk * 2 * NP, TOK = kScanChunk * kScanChannels * 4, YS = kScanChunk * kScanChannels;
+  constexpr int K = scan_buffers(NPL);
   pdl_wait();
   extern __shared__ __align__(16) float scan_smem[];
-  float* bc_s = scan_smem;                                  // [2][chunk][2 NP]: B, then C
-  float* tok_s = bc_s + 2 * BC;                             // [2][chunk][channels of the block][4]: dt, x, z, -
-  float* y_s = tok_s + 2 * TOK;                             // [2][chunk][channels of the block]
+  float* bc_s = scan_smem;                                  // [K][chunk][2 NP]: B, then C
+  float* tok_s = bc_s + K * BC;                             // [K][chunk][channels of the block][4]: dt, x, z, -
+  float* y_s = tok_s + K * TOK;                             // [2][chunk][channels of the block]
   const int e = blockIdx.y, c0 = blockIdx.x * kScanChannels;
-  const int tid = threadIdx.x, lane = tid % kScanLanes, ch = tid / kScanLanes;
+  const bool walker = threadIdx.x < kScanWalkers;
+  const int tid = walker ? threadIdx.x : threadIdx.x - kScanWalkers;      // place among the walkers, or among the helpers
+  const int lane = tid % kScanLanes, ch = tid / kScanLanes;
   const int c = c0 + ch;
   const bool live = c < channels;
   const int t0 = cu_q[e], q_len = cu_q[e + 1] - t0;
   float* slot = state + (size_t)slots[e] * state_stride;
-  float S[NPL], a[NPL];                                     // a lane's states are neighbours: n = lane * NPL + k
-#pragma unroll
-  for (int k = 0; k < NPL; ++k) {
-    const int n = lane * NPL + k;
-    const bool on = live && n < N;
-    S[k] = on ? slot[(size_t)c * N + n] : 0.f;
-    a[k] = on ? A[(size_t)c * N + n] * kLog2e : 0.f;        // exp(dt A) = 2^(dt A log2 e)
-  }
   const int n_chunks = (q_len + kScanChunk - 1) / kScanChunk;
 
+  // helpers: the fetch of chunk j, one group of copies (an empty one behind the last chunk)
   auto stage = [&](int j) {
+    if (j >= n_chunks) {
+      scan_cp_async_commit();
+      return;
+    }
     const int base = j * kScanChunk, n_here = min(kScanChunk, q_len - base);
-    float* bc = bc_s + (j & 1) * BC;
-    float* tk = tok_s + (j & 1) * TOK;
-    for (int idx = tid; idx < kScanChunk * 2 * NP; idx += blockDim.x) {
+    float* bc = bc_s + (j % K) * BC;
+    float* tk = tok_s + (j % K) * TOK;
+    for (int idx = tid; idx < kScanChunk * 2 * NP; idx += kScanWalkers) {
       const int i = idx / (2 * NP), r = idx - i * 2 * NP, half = r / NP, n = r - half * NP;
       if (i < n_here && n < N) scan_cp_async_4(bc + idx, dbc + (size_t)(t0 + base + i) * ld_dbc + b_off + half * N + n);
       else bc[idx] = 0.f;
     }
-    for (int idx = tid; idx < kScanChunk * kScanChannels; idx += blockDim.x) {
+    for (int idx = tid; idx < kScanChunk * kScanChannels; idx += kScanWalkers) {
       const int i = idx / kScanChannels, cc = idx - i * kScanChannels;
       float* dst = tk + (size_t)idx * 4;
       if (i < n_here && c0 + cc < channels) {
@@ -250,12 +263,23 @@ selective_scan_kernel(const float* __restrict__ x, const float* __restrict__ xz,
     }
     scan_cp_async_commit();
   };
-  // y of chunk j, gated and written: out = (y + D x) * silu(z)
+  // helpers: the step sizes of chunk j, once it has landed (a helper's own copies: no barrier between); `behind`
+  // groups were committed after the chunk's own
+  auto prepare = [&](int j, auto behind) {
+    const int n_here = min(kScanChunk, q_len - j * kScanChunk);
+    float* tk = tok_s + (j % K) * TOK;
+    scan_cp_async_wait<decltype(behind)::value>();
+    for (int idx = tid; idx < kScanChunk * kScanChannels; idx += kScanWalkers) {
+      const int i = idx / kScanChannels, cc = idx - i * kScanChannels;
+      if (i < n_here && c0 + cc < channels) tk[idx * 4] = softplus_f(tk[idx * 4] + (dt_bias ? dt_bias[c0 + cc] : 0.f));
+    }
+  };
+  // helpers: y of chunk j, gated and written: out = (y + D x) * silu(z)
   auto finish = [&](int j) {
     const int base = j * kScanChunk, n_here = min(kScanChunk, q_len - base);
-    const float* tk = tok_s + (j & 1) * TOK;
+    const float* tk = tok_s + (j % K) * TOK;
     const float* ys = y_s + (j & 1) * YS;
-    for (int idx = tid; idx < n_here * kScanChannels; idx += blockDim.x) {
+    for (int idx = tid; idx < n_here * kScanChannels; idx += kScanWalkers) {
       const int i = idx / kScanChannels, cc = idx - i * kScanChannels;
       if (c0 + cc < channels) {
         const float xv = tk[idx * 4 + 1], z = tk[idx * 4 + 2];
@@ -264,21 +288,31 @@ selective_scan_kernel(const float* __restrict__ x, const float* __restrict__ xz,
     }
   };
 
-  if (n_chunks > 0) stage(0);
-  for (int j = 0; j < n_chunks; ++j) {
-    const int base = j * kScanChunk, n_here = min(kScanChunk, q_len - base);
-    float* bc = bc_s + (j & 1) * BC;
-    float* tk = tok_s + (j & 1) * TOK;
-    float* ys = y_s + (j & 1) * YS;
-    scan_cp_async_wait<0>();
-    __syncthreads();                                        // chunk j has landed; the walk over chunk j - 1 is over
-    for (int idx = tid; idx < kScanChunk * kScanChannels; idx += blockDim.x) {
-      const int i = idx / kScanChannels, cc = idx - i * kScanChannels;
-      if (i < n_here && c0 + cc < channels) tk[idx * 4] = softplus_f(tk[idx * 4] + (dt_bias ? dt_bias[c0 + cc] : 0.f));
+  float S[NPL], a[NPL];                                     // a lane's states are neighbours: n = lane * NPL + k
+  if (walker) {
+#pragma unroll
+    for (int k = 0; k < NPL; ++k) {
+      const int n = lane * NPL + k;
+      const bool on = live && n < N;
+      S[k] = on ? slot[(size_t)c * N + n] : 0.f;
+      a[k] = on ? A[(size_t)c * N + n] * kLog2e : 0.f;      // exp(dt A) = 2^(dt A log2 e)
     }
-    if (j > 0) finish(j - 1);
-    __syncthreads();                                        // the other buffer is free again
-    if (j + 1 < n_chunks) stage(j + 1);
+  } else if (n_chunks > 0) {
+    for (int j = 0; j < K - 1; ++j) stage(j);
+    prepare(0, std::integral_constant<int, K - 2>());
+  }
+  for (int j = 0; j < n_chunks; ++j) {
+    __syncthreads();       // chunk j lies prepared; the walk over chunk j - 1 is over and its y lies in its buffer
+    if (!walker) {
+      if (j + 1 < n_chunks) prepare(j + 1, std::integral_constant<int, K - 3>());
+      if (j > 0) finish(j - 1);
+      stage(j + K - 1);                                     // into the buffer of chunk j - 1
+      continue;
+    }
+    const int n_here = min(kScanChunk, q_len - j * kScanChunk);
+    const float* bc = bc_s + (j % K) * BC;
+    const float* tk = tok_s + (j % K) * TOK;
+    float* ys = y_s + (j & 1) * YS;
 #pragma unroll 1
     for (int i0 = 0; i0 < n_here; i0 += GROUP) {
       float y[GROUP];
@@ -323,7 +357,10 @@ selective_scan_kernel(const float* __restrict__ x, const float* __restrict__ xz,
   }
   pdl_trigger();             // a long walk: the kernel behind would only sit on the SMs meanwhile
   __syncthreads();
-  if (n_chunks > 0) finish(n_chunks - 1);
+  if (!walker) {
+    if (n_chunks > 0) finish(n_chunks - 1);
+    return;
+  }
 #pragma unroll
   for (int k = 0; k < NPL; ++k) {
     const int n = lane * NPL + k;
@@ -469,18 +506,25 @@ extern "C" int srlm_selective_scan(const float* x, const float* xz, long long ld
   int npl = 1;
   while (npl * kScanLanes < N) npl <<= 1;
   const bool early = max_q_len <= 4 * kScanChunk;      // a long walk starts on an empty GPU, its blocks spread evenly
-  // two buffers of a chunk: B | C up to the lanes' reach, four words per (token, channel), the block's y
-  const size_t smem = (size_t)2 * kScanChunk * (2 * npl * kScanLanes + 5 * kScanChannels) * sizeof(float);
+  // some buffers of a chunk's operands (B | C up to the lanes' reach, four words per (token, channel)), two of the block's y
+  const size_t smem = (size_t)kScanChunk * (scan_buffers(npl) * (2 * npl * kScanLanes + 4 * kScanChannels) + 2 * kScanChannels) * sizeof(float);
 #define SRLM_SCAN(TO, NPL)                                                                                              \
-  launch_pdl_if(early, selective_scan_kernel<TO, NPL>, grid, dim3(kScanLanes * kScanChannels), smem, stream, x, xz, ld_xz, dbc, ld_dbc, \
-             b_off, dt_raw, dt_bias, A, D, state, state_stride, cu_q, slots, (TO*)out, channels, N, taps)
+  do {                                                                                                                  \
+    static bool sized = false;      /* the widest form asks for more shared memory than a kernel gets unasked */        \
+    if (!sized && smem > 48 * 1024) {                                                                                   \
+      cudaFuncSetAttribute(selective_scan_kernel<TO, NPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+      sized = true;                                                                                                     \
+    }                                                                                                                   \
+    launch_pdl_if(early, selective_scan_kernel<TO, NPL>, grid, dim3(kScanThreads), smem, stream, x, xz, ld_xz, dbc,     \
+                  ld_dbc, b_off, dt_raw, dt_bias, A, D, state, state_stride, cu_q, slots, (TO*)out, channels, N, taps); \
+  } while (0)
 #define SRLM_SCAN_N(TO)                                   \
   switch (npl) {                                          \
     case 1: SRLM_SCAN(TO, 1); break;                      \
     case 2: SRLM_SCAN(TO, 2); break;                      \
     case 4: SRLM_SCAN(TO, 4); break;                      \
     case 8: SRLM_SCAN(TO, 8); break;                      \
-    default: SRLM_SCAN(TO, 16); break;                    \
+    default: SRLM_SCAN(TO, 16);                           \
   }
   if (out_dtype == DT_F32) { SRLM_SCAN_N(float) }
   else if (out_dtype == DT_BF16) { SRLM_SCAN_N(bf16) }

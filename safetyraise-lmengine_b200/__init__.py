@@ -6,6 +6,7 @@ Public entry points: ``Engine`` (the step function), ``LLM`` (generation through
 the scheduler), ``SamplingParams``, and the command line
 ``python -m safetyraise_lmengine_b200 inspect|run|benchmark|replay``.
 """
+from .config import dovorax as _dovorax
 from .config import nekedra as _nekedra
 from .config import qwen3 as _qwen3
 from .config import pabalorn as _pabalorn
@@ -24,6 +25,8 @@ register_architecture(_qwen3.ARCHITECTURE, _qwen3.read_spec, _build_decoder, _qw
 register_architecture(_nekedra.ARCHITECTURE, _nekedra.read_spec, _build_decoder)
 register_architecture(_tonanex.ARCHITECTURE, _tonanex.read_spec, _build_decoder)
 register_architecture(_pabalorn.ARCHITECTURE, _pabalorn.read_spec, _build_decoder)
+
+register_architecture(_dovorax.ARCHITECTURE, _dovorax.read_spec, _build_decoder)
 
 __version__ = "0.1.0"
 

@@ -35,6 +35,11 @@ class PositionSpec:
     # l < original / high, divided by factor where l > original / low, and blended between the two with
     # s = (original / l - low) / (high - low): (1 - s) f / factor + s f.  None: the plain frequencies.
     scaling: Optional[Tuple[float, float, float, float]] = None
+    # a ramp over the pair index (factor, original, fast, slow): with index(n) = rotary_dim ln(original / (2 pi n)) /
+    # (2 ln theta), lo = max(floor(index(fast)), 0), hi = min(ceil(index(slow)), rotary_dim - 1) and r_i = clamp((i - lo) /
+    # max(hi - lo, 0.001), 0, 1), pair i turns at f_i (1 - r_i) + f_i r_i / factor, and cos and sin are multiplied by
+    # 0.1 ln(factor) + 1.  None: the plain frequencies and unit length.
+    ramp: Optional[Tuple[float, float, float, float]] = None
 
 
 @dataclass(frozen=True)
@@ -108,6 +113,9 @@ class SinkAttentionSpec(MixerSpec):
 @dataclass(frozen=True)
 class LatentAttentionNames:
     q: str = "mix.q"
+    q_down: str = "mix.dq"                  # with q_rank: the queries' own latent, its norm, and the up projection
+    q_norm: str = "mix.dq.norm"
+    q_up: str = "mix.uq"
     down: str = "mix.dkv"                   # rows: the latent (kv_rank), then the shared rotated key part (rot_dim)
     latent_norm: str = "mix.dkv.norm"
     up_k: str = "mix.uk"
@@ -130,6 +138,10 @@ class LatentAttentionSpec(MixerSpec):
     position: Optional[PositionSpec] = None  # rotation of the rot_dim part (its first rotary_dim elements)
     latent_norm_eps: float = 1e-6
     output_gate: bool = True                # head outputs times sigmoid of a per-head projection of the input
+    q_rank: int = 0                         # > 0: q = W_uq N(w, W_dq h), a latent of this size; 0: q = W_q h
+    window: Optional[int] = None            # what a query sees (None: every earlier key)
+    cache_window: Optional[int] = None      # what the cache keeps: the widest window of the steps that read the entry
+    own_kv: bool = True                     # False: no down projection; it reads the latent and key part another step cached
     names: LatentAttentionNames = LatentAttentionNames()
 
 
@@ -258,6 +270,101 @@ class SelectiveScanSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class ConvAttentionNames:
+    """Tensor names of an attention behind short convolutions, each appended to its layer's ``weight_prefix``; the
+    convolution of a projection is its weight's name + ``conv_suffix``, the per-head norm's weight + ``norm_suffix``."""
+    q: str = "mix.q"
+    k: str = "mix.k"
+    v: str = "mix.v"
+    o: str = "mix.o"
+    conv_suffix: str = ".conv"
+    norm_suffix: str = ".norm"
+
+
+@dataclass(frozen=True)
+class ConvAttentionSpec(MixerSpec):
+    """Grouped-query attention whose q, k and v each pass a short causal convolution over time (per channel, no bias)
+    right behind their projection; then a per-head RMS norm of q and k (one weight of head_dim for all heads), the
+    rotary encoding, and
+
+        p_ij = exp(s_ij) / (sink + sum_j' exp(s_ij')),   s_ij = (q_i . k_j) * softmax_scale,   0 <= i - j < window
+
+    with sink = 1 when ``unit_sink`` (one more key of score 0 and no value) and 0 otherwise.  The last conv_taps - 1
+    projected rows of a request are part of its state."""
+    hidden_size: int = 0
+    heads: int = 0
+    kv_heads: int = 0
+    head_dim: int = 0
+    v_head_dim: int = 0
+    softmax_scale: float = 0.0
+    conv_taps: int = 1
+    qk_norm_eps: Optional[float] = None     # None: q and k as convolved
+    position: Optional[PositionSpec] = None
+    unit_sink: bool = False
+    window: Optional[int] = None
+    names: ConvAttentionNames = ConvAttentionNames()
+
+
+@dataclass(frozen=True)
+class MatrixMemoryNames:
+    q: str = "mix.q"
+    k: str = "mix.k"
+    v: str = "mix.v"
+    gate: str = "mix.g"                     # [heads * v_head_dim, hidden]: the output gate
+    write: str = "mix.i"                    # [heads, hidden] and a bias (name + ".b"): the logarithm of the input gate
+    forget: str = "mix.f"                   # likewise: the forget gate ahead of its log-logistic
+    out_norm: str = "mix.norm"              # [heads * v_head_dim]
+    o: str = "mix.o"
+
+
+@dataclass(frozen=True)
+class MatrixMemorySpec(MixerSpec):
+    """A matrix of state S [head_dim, v_head_dim] and a vector n [head_dim] per head, with a running maximum m of the
+    gates' logarithms (m, S, n start at 0):  i = cap tanh((W_i h + b_i) / cap),  f = log logistic(cap tanh((W_f h + b_f) / cap)),
+
+        m' = max(f + m, i);  S <- exp(f + m - m') S + exp(i - m') k v^T;  n likewise with k;
+        o = S^T q / (max(|n . q|, exp(-m')) + denominator_floor),   q = W_q h / sqrt(head_dim)
+
+    then each head's o over its root mean square, times a weight over all heads, times logistic(W_g h), then W_o."""
+    hidden_size: int = 0
+    heads: int = 0
+    head_dim: int = 0
+    v_head_dim: int = 0
+    gate_cap: float = 0.0
+    norm_eps: float = 1e-6
+    denominator_floor: float = 1e-6
+    names: MatrixMemoryNames = MatrixMemoryNames()
+
+
+@dataclass(frozen=True)
+class GatedRecurrenceNames:
+    gate_branch: str = "mix.y"              # [width, hidden] and a bias (name + ".b")
+    recurrent_branch: str = "mix.x"         # likewise
+    conv: str = "mix.conv"                  # [width, taps] and a bias (name + ".b")
+    decay_gate: str = "mix.ra"              # [blocks, width / blocks, width / blocks] ([out, in]) and a bias [blocks, width / blocks]
+    input_gate: str = "mix.ri"              # likewise
+    decay: str = "mix.lam"                  # [width]
+    o: str = "mix.o"
+
+
+@dataclass(frozen=True)
+class GatedRecurrenceSpec(MixerSpec):
+    """A linear recurrence per channel with gates from block-diagonal products of its own input:
+
+        y = gelu_tanh(W_y h + b_y);   u = conv(W_x h + b_x) + b_conv      (a short causal convolution per channel)
+        r = logistic(R_a u + b_a);  i = logistic(R_i u + b_i)             (R block-diagonal, ``blocks`` square blocks)
+        a = exp(-decay_scale r softplus(lam));   S <- a S + sqrt(1 - a^2) i u;   out = W_o (S y)
+
+    S starts at zero, also for a request's first token.  S and the convolution's last taps - 1 inputs are the state."""
+    hidden_size: int = 0
+    width: int = 0
+    blocks: int = 1
+    conv_taps: int = 1
+    decay_scale: float = 8.0
+    names: GatedRecurrenceNames = GatedRecurrenceNames()
+
+
+@dataclass(frozen=True)
 class SideBySideSpec(MixerSpec):
     """Several mixers that read the same input; the result is the mean of their outputs, each first RMS-normed
     over the model width with a weight of its own (``out_norm_names``, appended to the layer's prefix)."""
@@ -265,6 +372,9 @@ class SideBySideSpec(MixerSpec):
     mixers: Tuple[MixerSpec, ...] = ()
     out_norm_names: Tuple[str, ...] = ()
     out_norm_eps: float = 1e-6
+    # "normed_mean": as above.  "weighted_sum": sum_k weights[k] * mixer_k(h), nothing normed (no out_norm_names).
+    combine: str = "normed_mean"
+    weights: Tuple[float, ...] = ()
 
 
 @dataclass(frozen=True)
@@ -274,6 +384,18 @@ class FeedForwardSpec:
     intermediate_size: int
     activation: str = "silu"
     names: GatedDenseNames = GatedDenseNames()   # read by the gated dense part; other kinds name their own
+
+
+@dataclass(frozen=True)
+class DenseNames:
+    up: str = "mlp.up"
+    down: str = "mlp.down"
+
+
+@dataclass(frozen=True)
+class DenseSpec(FeedForwardSpec):
+    """down(act(up(x))): no gate.  ``activation``: "gelu" (the exact one, with erf)."""
+    dense_names: DenseNames = DenseNames()
 
 
 @dataclass(frozen=True)
@@ -303,8 +425,14 @@ class RoutedExpertsSpec(FeedForwardSpec):
     shared_limit: float = 0.0
     # "softmax_of_chosen": weights = softmax over the chosen logits; "logistic": the logistic of each chosen
     # logit, not renormalised.  activation "silu": y = gate * logistic(gate) * up, no clamp (limit unused).
+    # "softmax_over_all": scores = softmax over every expert's logit; the experts form ``groups`` equal groups of
+    # neighbours, a group counts as its largest score, only experts of the best ``groups_kept`` groups can be chosen;
+    # weights = the chosen scores over their sum (+ 1e-20).
     scoring: str = "softmax_of_chosen"
     weight_on_input: bool = False           # a weight multiplies its expert's input instead of its output
+    groups: int = 1
+    groups_kept: int = 1
+    gated: bool = True                      # False: an expert is W_down act(W_up h) (activation "gelu"), and so is the shared one
     expert_names: RoutedExpertsNames = RoutedExpertsNames()
 
 
@@ -325,6 +453,7 @@ class LayerSpec:
     feed_forward_post_norm_name: str = "norm2b"
     mixer_gate_name: str = "rg1"             # weight [hidden, hidden]; its bias: this name + ".b"
     feed_forward_gate_name: str = "rg2"
+    residual_scale: float = 1.0              # block "post_norm": x <- norm(residual_scale * x + sublayer(x))
 
 
 @dataclass(frozen=True)

@@ -10,11 +10,22 @@
 //   latent_append  -- norm of c, rotation of kr, append to the pages;
 //   latent_absorb  -- per head [U_k^T q | rotated qr] as float32 queries of size rank + rot;
 //   latent_expand  -- per head U_v (sum p c), times the sigmoid of the head's output gate.
-// Rotation: element pairs (2i, 2i + 1), i < pairs, by the step's cos / sin tables [T, pairs]; the rest
-// of the rotated part passes unchanged.  All arithmetic float32.
+// Rotation: element pairs (2i, 2i + 1), or (i, i + pairs) when `halves` is set, i < pairs, by the step's cos / sin
+// tables [T, pairs]; the rest of the rotated part passes unchanged.  All arithmetic float32.
 #include "common.cuh"
 
 namespace srlm {
+
+// Element i of a rotated part `src` of token t (i < 2 * pairs).
+template <typename TP>
+__device__ __forceinline__ float rotated_element(const TP* __restrict__ src, int i, size_t t, int pairs, int halves,
+                                                 const float* __restrict__ cos_t, const float* __restrict__ sin_t) {
+  const int p = halves ? (i < pairs ? i : i - pairs) : (i >> 1);
+  const bool second = halves ? i >= pairs : (i & 1);
+  const float other = to_float(src[halves ? (second ? i - pairs : i + pairs) : (i ^ 1)]);
+  const float c = cos_t[t * pairs + p], s = sin_t[t * pairs + p], v = to_float(src[i]);
+  return second ? v * c + other * s : v * c - other * s;
+}
 
 constexpr int kTokTile = 16;
 
@@ -22,7 +33,7 @@ constexpr int kTokTile = 16;
 template <typename TP, typename TC>
 __global__ void latent_append_kernel(const TP* __restrict__ proj, long long ldp, int c_off,
                                      const float* __restrict__ norm_w, float eps, const float* __restrict__ cos_t,
-                                     const float* __restrict__ sin_t, int pairs, TC* __restrict__ cache,
+                                     const float* __restrict__ sin_t, int pairs, int halves, TC* __restrict__ cache,
                                      const int* __restrict__ kv_slot, int rank, int rot) {
   pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
   pdl_trigger();
@@ -38,12 +49,7 @@ __global__ void latent_append_kernel(const TP* __restrict__ proj, long long ldp,
   TC* row = cache + (size_t)kv_slot[t] * (rank + rot);      // one KV head: the flat slot is the row
   for (int i = threadIdx.x; i < rank; i += blockDim.x) row[i] = from_float<TC>(to_float(p[i]) * inv * norm_w[i]);
   for (int i = threadIdx.x; i < rot; i += blockDim.x) {
-    float v = to_float(p[rank + i]);
-    if (i < 2 * pairs) {
-      const float c = cos_t[(size_t)t * pairs + (i >> 1)], s = sin_t[(size_t)t * pairs + (i >> 1)];
-      const float other = to_float(p[rank + (i ^ 1)]);
-      v = (i & 1) ? v * c + other * s : v * c - other * s;
-    }
+    const float v = i < 2 * pairs ? rotated_element(p + rank, i, (size_t)t, pairs, halves, cos_t, sin_t) : to_float(p[rank + i]);
     row[rank + i] = from_float<TC>(v);
   }
 }
@@ -87,7 +93,7 @@ __device__ __forceinline__ void head_product(const float* __restrict__ in_s, int
 template <typename TP, typename TW>
 __global__ void __launch_bounds__(kProductWarps * 32)
 latent_absorb_kernel(const TP* __restrict__ proj, long long ldp, const TW* __restrict__ uk,
-                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pairs,
+                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pairs, int halves,
                      float* __restrict__ q_out, int T, int heads, int dim, int rot, int rank) {
   pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
   pdl_trigger();
@@ -114,13 +120,8 @@ latent_absorb_kernel(const TP* __restrict__ proj, long long ldp, const TW* __res
   for (int idx = threadIdx.x; idx < n * rot; idx += blockDim.x) {
     const int tt = idx / rot, i = idx - tt * rot, t = t0 + tt;
     const TP* src = proj + (size_t)t * ldp + (size_t)h * (dim + rot) + dim;
-    float v = to_float(src[i]);
-    if (i < 2 * pairs) {
-      const float c = cos_t[(size_t)t * pairs + (i >> 1)], s = sin_t[(size_t)t * pairs + (i >> 1)];
-      const float other = to_float(src[i ^ 1]);
-      v = (i & 1) ? v * c + other * s : v * c - other * s;
-    }
-    q_out[((size_t)t * heads + h) * qd + rank + i] = v;
+    q_out[((size_t)t * heads + h) * qd + rank + i] =
+        i < 2 * pairs ? rotated_element(src, i, (size_t)t, pairs, halves, cos_t, sin_t) : to_float(src[i]);
   }
 }
 
@@ -180,7 +181,7 @@ __global__ void latent_gather_kernel(const TC* __restrict__ cache, TC* __restric
 // q_out float32 [T, heads, dim + rot]: the unrotated part as projected, the rest rotated.
 template <typename TP>
 __global__ void latent_rotate_q_kernel(const TP* __restrict__ proj, long long ldp, const float* __restrict__ cos_t,
-                                       const float* __restrict__ sin_t, int pairs, float* __restrict__ q_out,
+                                       const float* __restrict__ sin_t, int pairs, int halves, float* __restrict__ q_out,
                                        int heads, int dim, int rot) {
   pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
   pdl_trigger();
@@ -188,14 +189,9 @@ __global__ void latent_rotate_q_kernel(const TP* __restrict__ proj, long long ld
   for (int idx = threadIdx.x; idx < heads * hd; idx += blockDim.x) {
     const int h = idx / hd, i = idx - h * hd;
     const TP* src = proj + (size_t)t * ldp + (size_t)h * hd;
-    float v = to_float(src[i]);
     const int r = i - dim;
-    if (r >= 0 && r < 2 * pairs) {
-      const float c = cos_t[(size_t)t * pairs + (r >> 1)], s = sin_t[(size_t)t * pairs + (r >> 1)];
-      const float other = to_float(src[dim + (r ^ 1)]);
-      v = (r & 1) ? v * c + other * s : v * c - other * s;
-    }
-    q_out[(size_t)t * heads * hd + idx] = v;
+    q_out[(size_t)t * heads * hd + idx] =
+        (r >= 0 && r < 2 * pairs) ? rotated_element(src + dim, r, (size_t)t, pairs, halves, cos_t, sin_t) : to_float(src[i]);
   }
 }
 
@@ -249,19 +245,19 @@ using namespace srlm;
   } while (0)
 
 extern "C" int srlm_latent_append(const void* proj, int proj_dtype, long long ldp, int c_off, const float* norm_w,
-                                  float eps, const float* cos_t, const float* sin_t, int pairs, void* cache,
+                                  float eps, const float* cos_t, const float* sin_t, int pairs, int halves, void* cache,
                                   int cache_dtype, const int* kv_slot, int T, int rank, int rot, cudaStream_t stream) {
   if (T <= 0) return ST_OK;
   if (rank <= 0 || rot < 0 || 2 * pairs > rot || c_off < 0 || ldp < c_off + rank + rot || !(eps > 0.f) ||
       (pairs > 0 && (!cos_t || !sin_t)))
     return refuse(ST_BAD_SIZE, "latent_append: rank=%d rot=%d pairs=%d c_off=%d ldp=%lld", rank, rot, pairs, c_off, ldp);
   SRLM_LATENT_TYPES(proj_dtype, cache_dtype, (launch_pdl(latent_append_kernel<TP, TW>, dim3(T), dim3(128), 0, stream, 
-      (const TP*)proj, ldp, c_off, norm_w, eps, cos_t, sin_t, pairs, (TW*)cache, kv_slot, rank, rot)));
+      (const TP*)proj, ldp, c_off, norm_w, eps, cos_t, sin_t, pairs, halves, (TW*)cache, kv_slot, rank, rot)));
   return launched();
 }
 
 extern "C" int srlm_latent_absorb(const void* proj, int proj_dtype, long long ldp, const void* uk, int w_dtype,
-                                  const float* cos_t, const float* sin_t, int pairs, float* q_out, int T, int heads,
+                                  const float* cos_t, const float* sin_t, int pairs, int halves, float* q_out, int T, int heads,
                                   int dim, int rot, int rank, cudaStream_t stream) {
   if (T <= 0) return ST_OK;
   const size_t smem = ((size_t)kTokTile * dim + (size_t)kProductWarps * kTokTile * kColTile) * sizeof(float);
@@ -271,7 +267,7 @@ extern "C" int srlm_latent_absorb(const void* proj, int proj_dtype, long long ld
                   pairs, ldp);
   dim3 grid((T + kTokTile - 1) / kTokTile, heads, (rank + kColTile - 1) / kColTile);
   SRLM_LATENT_TYPES(proj_dtype, w_dtype, (launch_pdl(latent_absorb_kernel<TP, TW>, dim3(grid), dim3(kProductWarps * 32), smem, stream, 
-      (const TP*)proj, ldp, (const TW*)uk, cos_t, sin_t, pairs, q_out, T, heads, dim, rot, rank)));
+      (const TP*)proj, ldp, (const TW*)uk, cos_t, sin_t, pairs, halves, q_out, T, heads, dim, rot, rank)));
   return launched();
 }
 
@@ -310,14 +306,14 @@ extern "C" int srlm_latent_gather(const void* cache, int cache_dtype, void* dst,
 }
 
 extern "C" int srlm_latent_rotate_q(const void* proj, int proj_dtype, long long ldp, const float* cos_t,
-                                    const float* sin_t, int pairs, float* q_out, int T, int heads, int dim, int rot,
+                                    const float* sin_t, int pairs, int halves, float* q_out, int T, int heads, int dim, int rot,
                                     cudaStream_t stream) {
   if (T <= 0) return ST_OK;
   if (heads <= 0 || dim <= 0 || rot < 0 || 2 * pairs > rot || ldp < (long long)heads * (dim + rot) ||
       (pairs > 0 && (!cos_t || !sin_t)))
     return refuse(ST_BAD_SIZE, "latent_rotate_q: heads=%d dim=%d rot=%d pairs=%d ldp=%lld", heads, dim, rot, pairs, ldp);
   SRLM_DISPATCH_ACT(proj_dtype, TP, (launch_pdl(latent_rotate_q_kernel<TP>, dim3(T), dim3(256), 0, stream, 
-      (const TP*)proj, ldp, cos_t, sin_t, pairs, q_out, heads, dim, rot)));
+      (const TP*)proj, ldp, cos_t, sin_t, pairs, halves, q_out, heads, dim, rot)));
   return launched();
 }
 

@@ -26,9 +26,11 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, float* __re
   sin_out[idx] = (float)s;
 }
 
-// The same table from given frequencies (float64 [half], e.g. rescaled ones): angle = position * freq[i].
+// The same table from given frequencies (float64 [half], e.g. rescaled ones): angle = position * freq[i]; cos and sin
+// times `length` (1: plain unit vectors).
 __global__ void rope_table_freq_kernel(const int* __restrict__ positions, const double* __restrict__ freq,
-                                       float* __restrict__ cos_out, float* __restrict__ sin_out, int T, int half) {
+                                       float* __restrict__ cos_out, float* __restrict__ sin_out, int T, int half,
+                                       double length) {
   pdl_wait();
   pdl_trigger();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -36,8 +38,8 @@ __global__ void rope_table_freq_kernel(const int* __restrict__ positions, const 
   const int t = idx / half, i = idx % half;
   double s, c;
   sincos((double)positions[t] * freq[i], &s, &c);
-  cos_out[idx] = (float)c;
-  sin_out[idx] = (float)s;
+  cos_out[idx] = (float)(c * length);
+  sin_out[idx] = (float)(s * length);
 }
 
 // One warp per (token, head) of the fused projection output
@@ -208,11 +210,12 @@ extern "C" int srlm_rope_table(const int* positions, float* cos_out, float* sin_
 
 // freq: float64 [half] on the device
 extern "C" int srlm_rope_table_freq(const int* positions, const double* freq, float* cos_out, float* sin_out, int T,
-                                    int half, cudaStream_t stream) {
+                                    int half, double length, cudaStream_t stream) {
   if (T <= 0) return ST_OK;
   if (half <= 0 || !freq) return refuse(ST_BAD_SIZE, "rope_table_freq: half=%d", half);
   const int n = T * half;
-  launch_pdl(rope_table_freq_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, positions, freq, cos_out, sin_out, T, half);
+  launch_pdl(rope_table_freq_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, positions, freq, cos_out, sin_out, T, half,
+             length);
   return launched();
 }
 

@@ -1,6 +1,8 @@
 // A feed-forward of routed experts: every token runs the `top` experts with the largest router logits and
 // adds their outputs, weighted by the softmax over those logits alone (scoring 0), or by the logistic of each
-// chosen logit, not renormalised (scoring 1).  A weight multiplies its expert's output (in `combine`) or, for
+// chosen logit, not renormalised (scoring 1), or by the softmax over ALL experts' logits, renormalised over the chosen
+// ones (scoring 2; the experts may then form equal groups of neighbours of which only the best few, judged by their
+// largest score, can be chosen).  A weight multiplies its expert's output (in `combine`) or, for
 // experts without biases, its input: then the first grouped product scales its gate and up sums by the pair's
 // weight before the activation (W (w h) = w (W h)), and `combine` adds the rows as they are.
 //
@@ -34,16 +36,57 @@ __device__ __forceinline__ float clamped_glu(float gate, float up, float limit, 
   return g * (1.f / (1.f + expf(-alpha * g))) * (u + 1.f);
 }
 
+// The activation of an expert without a gate: 0 none, 1 the exact gelu.
+__device__ __forceinline__ float plain_activation(float z, int act) {
+  return act == 1 ? 0.5f * z * (1.f + erff(z * 0.70710678118654752440f)) : z;
+}
+
 // One warp routes a token.  The row of logits sits in shared memory (z: E floats of the warp's own); `top` times
 // the warp takes the largest value left (ties: the lowest index) and strikes it out.  weights = softmax over the
 // chosen values; scoring 1: weight = logistic of the chosen value itself.
 __device__ __forceinline__ void route_token(const float* __restrict__ logits, long long ld, const float* __restrict__ bias,
                                             int t, int E, int top, float* z, int* __restrict__ choice,
-                                            float* __restrict__ weight, int scoring) {
+                                            float* __restrict__ weight, int scoring, int groups, int kept) {
   const int lane = threadIdx.x & 31;
   for (int e = lane; e < E; e += 32) z[e] = logits[(size_t)t * ld + e] + (bias ? bias[e] : 0.f);
   __syncwarp();
   float first = 0.f, sum = 0.f;
+  float z_max = 0.f, z_den = 1.f;          // scoring 2: score(e) = exp(z[e] - z_max) / z_den
+  if (scoring == 2) {
+    float mx = -CUDART_INF_F;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+    z_max = warp_max(mx);
+    float den = 0.f;
+    for (int e = lane; e < E; e += 32) den += expf(z[e] - z_max);
+    z_den = warp_sum(den);
+    if (groups > 1 && kept < groups) {
+      // a group counts as its largest logit (the softmax keeps the order); `kept` times the best group left is marked
+      // (ties: the lowest index); the experts of unmarked groups are struck out.  Lane l owns groups l, l + 32, ...
+      const int per = E / groups;
+      uint32_t mine = 0;
+      for (int c = 0; c < kept; ++c) {
+        float best = -CUDART_INF_F;
+        int at = groups;
+        for (int g = lane, i = 0; g < groups; g += 32, ++i) {
+          if ((mine >> i) & 1u) continue;
+          float gm = -CUDART_INF_F;
+          for (int e = g * per; e < (g + 1) * per; ++e) gm = fmaxf(gm, z[e]);
+          if (gm > best || (gm == best && g < at)) { best = gm; at = g; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+          const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+          if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at < groups && (at & 31) == lane) mine |= 1u << (at >> 5);
+      }
+      for (int g = lane, i = 0; g < groups; g += 32, ++i)
+        if (!((mine >> i) & 1u))
+          for (int e = g * per; e < (g + 1) * per; ++e) z[e] = -CUDART_INF_F;
+      __syncwarp();
+    }
+  }
   for (int c = 0; c < top; ++c) {
     float best = -CUDART_INF_F;
     int at = E;
@@ -59,7 +102,7 @@ __device__ __forceinline__ void route_token(const float* __restrict__ logits, lo
     }
     if (at >= E) at = c < E ? c : 0;            // a row of NaN: any valid expert; the step's finite check reports it
     if (c == 0) first = best;
-    const float p = scoring == 1 ? 1.f / (1.f + expf(-best)) : expf(best - first);
+    const float p = scoring == 1 ? 1.f / (1.f + expf(-best)) : scoring == 2 ? expf(best - z_max) / z_den : expf(best - first);
     sum += p;
     if (lane == 0) {
       choice[(size_t)t * top + c] = at;
@@ -71,18 +114,21 @@ __device__ __forceinline__ void route_token(const float* __restrict__ logits, lo
   __syncwarp();
   if (scoring == 0)
     for (int c = lane; c < top; c += 32) weight[(size_t)t * top + c] /= sum;
+  if (scoring == 2)
+    for (int c = lane; c < top; c += 32) weight[(size_t)t * top + c] /= sum + 1e-20f;
   __syncwarp();
 }
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ bias,
-                                 int T, int E, int top, int* __restrict__ choice, float* __restrict__ weight, int scoring) {
+                                 int T, int E, int top, int* __restrict__ choice, float* __restrict__ weight, int scoring,
+                                 int groups, int kept) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ float route_smem[];
   const int warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   const int t = blockIdx.x * warps + warp;
   if (t >= T) return;
-  route_token(logits, ld, bias, t, E, top, route_smem + (size_t)warp * E, choice, weight, scoring);
+  route_token(logits, ld, bias, t, E, top, route_smem + (size_t)warp * E, choice, weight, scoring, groups, kept);
 }
 
 // One block.  offsets[E + 1]: first row of each expert; tiles[E + 1]: first tile of each expert (tiles of
@@ -97,7 +143,7 @@ __global__ void moe_sort_kernel(int* __restrict__ choice, int n, int E, int tile
                                 int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ pair_of_row,
                                 int* __restrict__ row_of_pair, int* __restrict__ group_of_tile, int max_tiles, int rows_cap,
                                 const float* __restrict__ logits, long long ld, const float* __restrict__ bias, int top,
-                                float* __restrict__ weight, int scoring) {
+                                float* __restrict__ weight, int scoring, int groups, int kept) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ int sort_smem[];
@@ -105,7 +151,7 @@ __global__ void moe_sort_kernel(int* __restrict__ choice, int n, int E, int tile
   int* start = count + E;            // [E + 1]
   if (logits) {
     float* z = reinterpret_cast<float*>(start + E + 1) + (size_t)(threadIdx.x >> 5) * E;
-    for (int t = threadIdx.x >> 5; t < n / top; t += blockDim.x >> 5) route_token(logits, ld, bias, t, E, top, z, choice, weight, scoring);
+    for (int t = threadIdx.x >> 5; t < n / top; t += blockDim.x >> 5) route_token(logits, ld, bias, t, E, top, z, choice, weight, scoring, groups, kept);
     __syncthreads();                 // the choices of all tokens are written (and visible to the block)
   }
   for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
@@ -201,7 +247,7 @@ __global__ void __launch_bounds__(256)
 moe_grouped_simt_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ pair_of_row, int pairs_per_token,
                         const TW* __restrict__ W, TO* __restrict__ C, long long ldc, const int* __restrict__ offsets,
                         const int* __restrict__ tiles, int E, int N, int K, int interleaved, float limit, float alpha,
-                        const float* __restrict__ pair_scale) {
+                        const float* __restrict__ pair_scale, int act) {
   pdl_wait();
   pdl_trigger();
   __shared__ float As[GBK][kTile + 4];
@@ -268,7 +314,8 @@ moe_grouped_simt_kernel(const TA* __restrict__ A, long long lda, const int* __re
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tn + j;
       if (n >= N) continue;
-      const float v = GLU ? clamped_glu(acc[i][j] * ws, acu[GLU ? i : 0][j] * ws, limit, alpha) : acc[i][j];
+      const float v = GLU ? clamped_glu(acc[i][j] * ws, acu[GLU ? i : 0][j] * ws, limit, alpha)
+                          : plain_activation(acc[i][j], act);
       C[(size_t)row * ldc + n] = from_float<TO>(v);
     }
   }
@@ -303,7 +350,7 @@ __global__ void __launch_bounds__(256)
 moe_grouped_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ pair_of_row, int pairs_per_token,
                        const bf16* __restrict__ W, TO* __restrict__ C, long long ldc, const int* __restrict__ offsets,
                        const int* __restrict__ tiles, int E, int NW, int K, float limit, float alpha,
-                       const float* __restrict__ pair_scale) {
+                       const float* __restrict__ pair_scale, int act) {
   pdl_wait();
   pdl_trigger();
   // NW: weight rows per expert (twice the features when GLU)
@@ -392,7 +439,7 @@ moe_grouped_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __r
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             const int n = n0 + wn * 32 + j * 8 + (lane & 3) * 2 + c;
-            if (n < NW) C[(size_t)row * ldc + n] = from_float<TO>(acc[i][j][2 * half + c]);
+            if (n < NW) C[(size_t)row * ldc + n] = from_float<TO>(plain_activation(acc[i][j][2 * half + c], act));
           }
       }
     }
@@ -437,16 +484,26 @@ using namespace srlm;
 extern "C" int srlm_moe_tile_rows() { return kTile; }
 
 // logits float32 [T, ld >= E]; bias float32 [E] or null; choice int32 [T, top]; weight float32 [T, top]
-// scoring 0: weights = softmax over the chosen logits; 1: the logistic of each chosen logit
+// scoring 0: weights = softmax over the chosen logits; 1: the logistic of each chosen logit; 2: the softmax over all
+// logits, renormalised over the chosen ones, the choice limited to the best `kept` of `groups` equal groups of neighbours
+static int routing_ok(const char* what, int E, int top, int scoring, int groups, int kept) {
+  if (scoring < 0 || scoring > 2 || groups <= 0 || kept <= 0 || kept > groups || E % groups || groups > 1024 ||
+      (groups > 1 && scoring != 2) || (long long)top > (long long)(E / groups) * kept)
+    return refuse(ST_BAD_SIZE, "%s: scoring %d, %d experts in %d groups of which %d are kept, top %d", what, scoring, E, groups,
+                  kept, top);
+  return ST_OK;
+}
+
 extern "C" int srlm_moe_route(const float* logits, long long ld, const float* bias, int T, int E, int top, int* choice,
-                              float* weight, int scoring, cudaStream_t stream) {
+                              float* weight, int scoring, int groups, int kept, cudaStream_t stream) {
   if (T <= 0) return ST_OK;
-  if (E <= 0 || top <= 0 || top > E || ld < E || E > 8192 || scoring < 0 || scoring > 1)
+  if (E <= 0 || top <= 0 || top > E || ld < E || E > 8192)
     return refuse(ST_BAD_SIZE, "moe_route: experts=%d top=%d ld=%lld (at most 8192 experts)", E, top, ld);
+  if (int r = routing_ok("moe_route", E, top, scoring, groups, kept)) return r;
   int warps = 4;
   while (warps > 1 && (size_t)warps * E * sizeof(float) > 40 * 1024) warps >>= 1;
   launch_pdl(moe_route_kernel, dim3((T + warps - 1) / warps), dim3(warps * 32), (size_t)warps * E * sizeof(float), stream,
-             logits, ld, bias, T, E, top, choice, weight, scoring);
+             logits, ld, bias, T, E, top, choice, weight, scoring, groups, kept);
   return launched();
 }
 
@@ -461,9 +518,11 @@ extern "C" int srlm_moe_sort_routes(int tokens, int E) { return tokens <= 512 &&
 extern "C" int srlm_moe_sort(int* choice, int n, int E, int* offsets, int* tiles, int* pair_of_row,
                              int* row_of_pair, int tile_rows, int* group_of_tile, int max_tiles, int rows_cap,
                              const float* logits, long long ld, const float* bias, int top, float* weight, int scoring,
-                             cudaStream_t stream) {
+                             int groups, int kept, cudaStream_t stream) {
   if (n <= 0) return ST_OK;
   if (E <= 0 || E > 4096) return refuse(ST_BAD_SIZE, "moe_sort: experts=%d (at most 4096)", E);
+  if (logits)
+    if (int r = routing_ok("moe_sort", E, top, scoring, groups, kept)) return r;
   if (logits && (top <= 0 || top > E || n % top || ld < E || !weight || !srlm_moe_sort_routes(n / top, E)))
     return refuse(ST_BAD_SIZE, "moe_sort: routing %d pairs, top=%d of %d experts, ld=%lld", n, top, E, ld);
   const int align = tile_rows > 0;
@@ -474,7 +533,7 @@ extern "C" int srlm_moe_sort(int* choice, int n, int E, int* offsets, int* tiles
   const size_t smem = (size_t)(2 * E + 1) * sizeof(int) + (logits ? (size_t)32 * E * sizeof(float) : 0);
   launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), smem, stream, choice, n, E,
              align ? tile_rows : kTile, align, offsets, tiles, pair_of_row, row_of_pair, group_of_tile, max_tiles, rows_cap,
-             logits, ld, bias, top, weight, scoring);
+             logits, ld, bias, top, weight, scoring, groups, kept);
   return launched();
 }
 
@@ -497,12 +556,13 @@ static inline int tile_bound(int n, int E) {
   return (int)(by_rows < n ? by_rows : n);
 }
 
-// glu != 0: W [E, 2 N, K], C [n, N] = the experts' activation; else W [E, N, K], C [n, N] = the product.
+// glu != 0: W [E, 2 N, K], C [n, N] = the experts' activation; else W [E, N, K], C [n, N] = the product, through the
+// exact gelu when act == 1.
 // pair_of_row null: row r of A is row r of C (the experts' second product); else A's row is the pair's token.
 extern "C" int srlm_moe_grouped_simt(const void* A, int a_dtype, long long lda, const int* pair_of_row, int pairs_per_token,
                                      const void* W, int w_dtype, void* C, int c_dtype, long long ldc, const int* offsets,
                                      const int* tiles, int n, int E, int N, int K, int glu, int interleaved, float limit,
-                                     float alpha, const float* pair_scale, cudaStream_t stream) {
+                                     float alpha, const float* pair_scale, int act, cudaStream_t stream) {
   if (n <= 0) return ST_OK;
   if (E <= 0 || N <= 0 || K <= 0 || lda < K || ldc < N || (pair_of_row && pairs_per_token <= 0) ||
       (glu && interleaved && N % 8))
@@ -514,10 +574,10 @@ extern "C" int srlm_moe_grouped_simt(const void* A, int a_dtype, long long lda, 
   do {                                                                                                                \
     if (glu) launch_pdl(moe_grouped_simt_kernel<TA, TW, TO, true>, grid, dim3(256), 0, stream, (const TA*)A, lda,    \
                         pair_of_row, pairs_per_token, (const TW*)W, (TO*)C, ldc, offsets, tiles, E, N, K, interleaved, \
-                        limit, alpha, pair_scale);                                                                    \
+                        limit, alpha, pair_scale, act);                                                               \
     else launch_pdl(moe_grouped_simt_kernel<TA, TW, TO, false>, grid, dim3(256), 0, stream, (const TA*)A, lda,       \
                     pair_of_row, pairs_per_token, (const TW*)W, (TO*)C, ldc, offsets, tiles, E, N, K, interleaved,    \
-                    limit, alpha, pair_scale);                                                                        \
+                    limit, alpha, pair_scale, act);                                                                   \
   } while (0)
   if (a_dtype == DT_F32 && w_dtype == DT_F32 && c_dtype == DT_F32) SRLM_GROUPED(float, float, float);
   else if (a_dtype == DT_BF16 && w_dtype == DT_BF16 && c_dtype == DT_BF16) SRLM_GROUPED(bf16, bf16, bf16);
@@ -569,7 +629,7 @@ extern "C" int srlm_moe_grouped_mma_takes(int N, int K, int glu) { return K > 0 
 
 extern "C" int srlm_moe_grouped_mma(const void* A, long long lda, const int* pair_of_row, int pairs_per_token, const void* W,
                                     void* C, int c_dtype, long long ldc, const int* offsets, const int* tiles, int n, int E,
-                                    int N, int K, int glu, float limit, float alpha, const float* pair_scale,
+                                    int N, int K, int glu, float limit, float alpha, const float* pair_scale, int act,
                                     cudaStream_t stream) {
   if (n <= 0) return ST_OK;
   if (E <= 0 || !srlm_moe_grouped_mma_takes(N, K, glu) || lda < K || lda % 8 || ldc < N || (pair_of_row && pairs_per_token <= 0))
@@ -581,7 +641,7 @@ extern "C" int srlm_moe_grouped_mma(const void* A, long long lda, const int* pai
   dim3 grid((NW + MBN - 1) / MBN, bound);
 #define SRLM_GROUPED_MMA(TO, G)                                                                                          \
   launch_pdl(moe_grouped_mma_kernel<TO, G>, grid, dim3(256), 0, stream, (const bf16*)A, lda, pair_of_row, pairs_per_token, \
-             (const bf16*)W, (TO*)C, ldc, offsets, tiles, E, NW, K, limit, alpha, pair_scale)
+             (const bf16*)W, (TO*)C, ldc, offsets, tiles, E, NW, K, limit, alpha, pair_scale, act)
   if (c_dtype == DT_BF16 && glu) SRLM_GROUPED_MMA(bf16, true);
   else if (c_dtype == DT_F32 && glu) SRLM_GROUPED_MMA(float, true);
   else if (c_dtype == DT_BF16) SRLM_GROUPED_MMA(bf16, false);

@@ -194,13 +194,13 @@ class KernelLibrary:
         self._check(self.lib.srlm_rope_table(_ptr(positions), _ptr(cos), _ptr(sin), C.c_int(T), C.c_int(half),
                                              C.c_double(theta), C.c_int(rotary_dim), _stream()), "rope_table")
 
-    def rope_table_freq(self, positions, freq, cos, sin):
-        """cos / sin [T, half] of position * freq[i]; freq float64 [half] on the device."""
+    def rope_table_freq(self, positions, freq, cos, sin, length=1.0):
+        """cos / sin [T, half] of position * freq[i], times ``length``; freq float64 [half] on the device."""
         T, half = cos.shape
         if freq.dtype != torch.float64 or freq.numel() != half:
             raise ShapeError("rope_table_freq: one float64 frequency per pair")
         self._check(self.lib.srlm_rope_table_freq(_ptr(positions), _ptr(freq), _ptr(cos), _ptr(sin), C.c_int(T),
-                                                  C.c_int(half), _stream()), "rope_table_freq")
+                                                  C.c_int(half), C.c_double(length), _stream()), "rope_table_freq")
 
     def qk_norm_rope_append(self, qkv, q_out, k_cache, v_cache, q_norm_w, k_norm_w, eps, cos, sin, kv_slot,
                             nq, nkv, hd, rotary_half, write_kv=True, interleaved=False):
@@ -939,12 +939,15 @@ class KernelLibrary:
             raise ShapeError("float32 columns of a row-major CUDA tensor are wanted")
         return C.c_void_p(t.data_ptr() + 4 * column), C.c_longlong(t.stride(0))
 
-    ROUTER_SCORING = {"softmax_of_chosen": 0, "logistic": 1}
+    ROUTER_SCORING = {"softmax_of_chosen": 0, "logistic": 1, "softmax_over_all": 2}
 
-    def moe_route(self, logits, bias, top, choice, weight, column=0, experts=None, scoring="softmax_of_chosen"):
+    def moe_route(self, logits, bias, top, choice, weight, column=0, experts=None, scoring="softmax_of_chosen",
+                  groups=(1, 1)):
         """logits float32 [T, E] (+ bias float32 [E]) -> choice int32 [T, top], the experts with the largest
         logits (ties: the lowest index), and weight float32 [T, top]: the softmax over the chosen logits, or
-        (scoring "logistic") the logistic of each chosen logit, not renormalised.
+        (scoring "logistic") the logistic of each chosen logit, not renormalised, or (scoring "softmax_over_all") the
+        softmax over all logits, renormalised over the chosen ones; then groups = (count, kept): the experts form
+        ``count`` equal groups of neighbours and only experts of the ``kept`` groups with the largest scores are chosen.
         column / experts: the logits are those columns of a wider tensor."""
         T = logits.shape[0]
         E = logits.shape[1] - column if experts is None else experts
@@ -953,14 +956,15 @@ class KernelLibrary:
         ptr, ld = self._columns(logits, column, E)
         self._check(self.lib.srlm_moe_route(ptr, ld, _ptr(bias), C.c_int(T), C.c_int(E),
                                             C.c_int(top), _ptr(choice), _ptr(weight),
-                                            C.c_int(self.ROUTER_SCORING[scoring]), _stream()), "moe_route")
+                                            C.c_int(self.ROUTER_SCORING[scoring]), C.c_int(groups[0]), C.c_int(groups[1]),
+                                            _stream()), "moe_route")
 
     def moe_sort_routes(self, tokens, experts) -> bool:
         """Whether moe_sort(..., route=...) routes a step of this many tokens itself."""
         return bool(self.lib.srlm_moe_sort_routes(C.c_int(tokens), C.c_int(experts)))
 
     def moe_sort(self, choice, experts, offsets, tiles, pair_of_row, row_of_pair, tile_rows=0, group_of_tile=None,
-                 route=None, scoring="softmax_of_chosen"):
+                 route=None, scoring="softmax_of_chosen", groups=(1, 1)):
         """The (token, choice) pairs ordered by expert: offsets / tiles int32 [experts + 1] (first row and first
         tile of each expert), pair_of_row / row_of_pair int32 [pairs].  tile_rows > 0: every expert's rows start at
         a multiple of tile_rows; pair_of_row then covers all rows of group_of_tile's tiles (-1: a row without a
@@ -976,7 +980,8 @@ class KernelLibrary:
             _ptr(choice), C.c_int(choice.numel()), C.c_int(experts), _ptr(offsets), _ptr(tiles), _ptr(pair_of_row),
             _ptr(row_of_pair), C.c_int(tile_rows), _ptr(group_of_tile),
             C.c_int(group_of_tile.numel() if group_of_tile is not None else 0),
-            C.c_int(pair_of_row.numel()), *routing, C.c_int(self.ROUTER_SCORING[scoring]), _stream()), "moe_sort")
+            C.c_int(pair_of_row.numel()), *routing, C.c_int(self.ROUTER_SCORING[scoring]), C.c_int(groups[0]),
+            C.c_int(groups[1]), _stream()), "moe_sort")
 
     GROUPED_TILE = 128       # token rows of a tile of the grouped tensor-memory product (one SM a tile)
     GROUPED_PAIR_TILE = 256  # ... of its pair form (two SMs on 256 weight rows x 256 tokens)
@@ -1012,14 +1017,17 @@ class KernelLibrary:
             C.c_int(int(glu)),
             C.c_float(limit), C.c_float(alpha), _ptr(err), _stream()), "gemm_tn_tcgen05_grouped")
 
+    PLAIN_ACTIVATIONS = {None: 0, "gelu": 1}
+
     def moe_grouped(self, a, pair_of_row, pairs_per_token, w, out, offsets, tiles, glu=False, interleaved=False,
-                    limit=0.0, alpha=0.0, pair_scale=None):
+                    limit=0.0, alpha=0.0, pair_scale=None, act=None):
         """out[row] = a[row's token] . w[row's expert]^T for every row of the sorted pairs (pair_of_row None: row r
         of ``a`` is row r of ``out``).  w [experts, N, K]; glu: w [experts, 2 N, K] and out gets the clamped GLU of
         the gate and up halves (interleaved: in blocks of 8 gate rows and 8 up rows, else all gate rows first);
         limit 0: the plain GLU, gate * logistic(gate) * up.  pair_scale (float32, one number a pair; with glu): the
         gate and up sums of a row are multiplied by its pair's number ahead of the activation, which for experts
-        without biases is the activation of the scaled input."""
+        without biases is the activation of the scaled input.  act "gelu" (without glu): out gets the exact gelu of
+        the product."""
         E, rows, K = w.shape
         n, N = out.shape
         if a.shape[1] != K or rows != (2 * N if glu else N):
@@ -1030,14 +1038,14 @@ class KernelLibrary:
             self._check(self.lib.srlm_moe_grouped_mma(
                 _ptr(a), C.c_longlong(a.stride(0)), _ptr(pair_of_row), C.c_int(pairs_per_token), _ptr(w), _ptr(out),
                 dtype_code(out.dtype), C.c_longlong(out.stride(0)), _ptr(offsets), _ptr(tiles), C.c_int(n), C.c_int(E),
-                C.c_int(N), C.c_int(K), C.c_int(int(glu)), C.c_float(limit), C.c_float(alpha), _ptr(pair_scale), _stream()),
-                "moe_grouped_mma")
+                C.c_int(N), C.c_int(K), C.c_int(int(glu)), C.c_float(limit), C.c_float(alpha), _ptr(pair_scale),
+                C.c_int(self.PLAIN_ACTIVATIONS[act]), _stream()), "moe_grouped_mma")
             return
         self._check(self.lib.srlm_moe_grouped_simt(
             _ptr(a), dtype_code(a.dtype), C.c_longlong(a.stride(0)), _ptr(pair_of_row), C.c_int(pairs_per_token), _ptr(w),
             dtype_code(w.dtype), _ptr(out), dtype_code(out.dtype), C.c_longlong(out.stride(0)), _ptr(offsets), _ptr(tiles),
             C.c_int(n), C.c_int(E), C.c_int(N), C.c_int(K), C.c_int(int(glu)), C.c_int(int(interleaved)), C.c_float(limit),
-            C.c_float(alpha), _ptr(pair_scale), _stream()), "moe_grouped_simt")
+            C.c_float(alpha), _ptr(pair_scale), C.c_int(self.PLAIN_ACTIVATIONS[act]), _stream()), "moe_grouped_simt")
 
     def moe_combine(self, rows, row_of_pair, weight, shared, out):
         """out[t] = sum over t's choices, in their order, of weight * rows[row of the pair] (+ shared[t]); weight
@@ -1087,6 +1095,121 @@ class KernelLibrary:
                                                       dtype_code(a.dtype), dtype_code(out.dtype), C.c_int(T), C.c_int(H),
                                                       _stream()), "paired_rmsnorm_mean")
 
+    # ---- blocks that norm after the sum, and their elementwise companions ---------------------------
+    def postnorm_scale_add(self, residual, delta, weight, alpha, eps, unit_offset=False, out=None):
+        """residual <- w' * y / sqrt(mean(y^2) + eps) with y = alpha * residual + delta and w' = weight (or 1 + weight),
+        in place (float32 [T, H]); delta [T, H] in float32 or the activation dtype, or None; ``out``: a copy of the
+        new rows in its own dtype."""
+        T, H = residual.shape
+        if residual.dtype != torch.float32 or (delta is not None and tuple(delta.shape) != (T, H)) or \
+                (out is not None and tuple(out.shape) != (T, H)):
+            raise ShapeError(f"postnorm_scale_add: residual {tuple(residual.shape)} {residual.dtype}")
+        self._check(self.lib.srlm_postnorm_scale_add(
+            _ptr(residual), _ptr(delta), dtype_code(delta.dtype) if delta is not None else 0, _ptr(weight), C.c_float(alpha),
+            C.c_float(eps), C.c_int(int(unit_offset)), _ptr(out), dtype_code(out.dtype) if out is not None else 0,
+            C.c_int(T), C.c_int(H), _stream()), "postnorm_scale_add")
+
+    def rmsnorm_columns(self, x, column, width, weight, eps, out, unit_offset=False):
+        """out [T, width] = RMS norm over the columns [column, column + width) of x (float32, row-major), times weight
+        (float32 [width]; None: no weight)."""
+        ptr, ld = self._columns(x, column, width)
+        self._check(self.lib.srlm_rmsnorm_columns(ptr, ld, _ptr(weight), C.c_float(eps), C.c_int(int(unit_offset)), _ptr(out),
+                                                  dtype_code(out.dtype), C.c_int(x.shape[0]), C.c_int(width), _stream()),
+                    "rmsnorm_columns")
+
+    ACTIVATIONS = {"gelu": 0, "gelu_tanh": 1}
+
+    def activation(self, x, out, kind, bias=None, column=0):
+        """out [T, F] = act(x[:, column : column + F] + bias); kind "gelu" (exact) or "gelu_tanh"."""
+        T, F = out.shape
+        if not x.is_cuda or x.stride(1) != 1 or x.shape[1] < column + F:
+            raise ShapeError("activation: columns of a row-major CUDA tensor are wanted")
+        self._check(self.lib.srlm_activation(C.c_void_p(x.data_ptr() + x.element_size() * column), dtype_code(x.dtype),
+                                             C.c_longlong(x.stride(0)), _ptr(bias), _ptr(out), dtype_code(out.dtype),
+                                             C.c_int(T), C.c_int(F), C.c_int(self.ACTIVATIONS[kind]), _stream()), "activation")
+
+    def weighted_sum(self, a, wa, b, wb, out):
+        """out = wa * a + wb * b (a and b of one dtype, float32 sums)."""
+        if a.shape != b.shape or a.dtype != b.dtype or out.shape != a.shape:
+            raise ShapeError("weighted_sum: operands of one shape and dtype")
+        self._check(self.lib.srlm_weighted_sum(_ptr(a), C.c_float(wa), _ptr(b), C.c_float(wb), dtype_code(a.dtype),
+                                               _ptr(out), dtype_code(out.dtype), C.c_longlong(a.numel()), _stream()),
+                    "weighted_sum")
+
+    # ---- short convolutions over time ---------------------------------------------------------------
+    def short_conv(self, ctx, x, column, channels, weight, state, state_off, out, in_bias=None, out_bias=None, out_low=None):
+        """out float32 [T, channels] = the causal convolution over time of the columns [column, + channels) of x (float32),
+        per channel with weight float32 [channels, taps]; in_bias is added to every input, out_bias to every result.  A
+        portion's first tokens read the slot's carried inputs ([taps - 1][channels] floats at state_off of its row of
+        ``state``, float32 [slots, row]); ``conv_carry`` renews them afterwards.  out_low: a copy in its own dtype."""
+        ptr, ld = self._columns(x, column, channels)
+        self._check(self.lib.srlm_short_conv(
+            ptr, ld, _ptr(in_bias), _ptr(weight), _ptr(out_bias), _ptr(state), C.c_longlong(state.stride(0)),
+            C.c_int(state_off), _ptr(ctx.entry_of_token), _ptr(ctx.cu_q), _ptr(ctx.slots), _ptr(out), _ptr(out_low),
+            dtype_code(out_low.dtype) if out_low is not None else 0, C.c_int(x.shape[0]), C.c_int(channels),
+            C.c_int(weight.shape[1]), _stream()), "short_conv")
+
+    def conv_carry(self, ctx, x, column, channels, taps, state, state_off, in_bias=None):
+        """The slots' carried inputs of a short convolution <- the last taps - 1 inputs of every entry (what was carried
+        before counts as the inputs ahead of the portion)."""
+        if taps <= 1:
+            return
+        ptr, ld = self._columns(x, column, channels)
+        self._check(self.lib.srlm_conv_carry(ptr, ld, _ptr(in_bias), _ptr(state), C.c_longlong(state.stride(0)),
+                                             C.c_int(state_off), _ptr(ctx.cu_q), _ptr(ctx.slots), C.c_int(ctx.n_entries),
+                                             C.c_int(channels), C.c_int(taps), _stream()), "conv_carry")
+
+    def conv_norm_rope_append(self, ctx, proj, conv_w, state, state_off, q_norm_w, k_norm_w, eps, rotation, q_out, k_cache,
+                              v_cache, kv_slot, nq, nkv, dk, dv):
+        """From a stacked q | k | v projection (float32 [T, >= nq dk + nkv (dk + dv)]): every channel through its short
+        convolution (conv_w float32 [channels, taps], the slots' carried inputs in ``state``), every q and k head
+        RMS-normed with q_norm_w / k_norm_w (float32 [dk]; None: not normed) and its leading pairs turned; q to q_out
+        (float32 or bfloat16), k and v to the pages."""
+        pairs = rotation.pairs if rotation is not None else 0
+        self._check(self.lib.srlm_conv_norm_rope_append(
+            _ptr(proj), C.c_longlong(proj.stride(0)), _ptr(conv_w), _ptr(state), C.c_longlong(state.stride(0)),
+            C.c_int(state_off), _ptr(q_norm_w), _ptr(k_norm_w), C.c_float(eps or 0.0),
+            _ptr(rotation.cos if pairs else None), _ptr(rotation.sin if pairs else None), C.c_int(pairs),
+            C.c_int(int(bool(pairs and rotation.interleaved))), _ptr(ctx.entry_of_token), _ptr(ctx.cu_q), _ptr(ctx.slots),
+            _ptr(kv_slot), _ptr(q_out), dtype_code(q_out.dtype), _ptr(k_cache), _ptr(v_cache), dtype_code(k_cache.dtype),
+            C.c_int(proj.shape[0]), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv), C.c_int(k_cache.shape[2]),
+            C.c_int(conv_w.shape[1]), _stream()), "conv_norm_rope_append")
+
+    # ---- the matrix memory ----------------------------------------------------------------------------
+    def matrix_memory_recurrence(self, ctx, proj, bias_i, bias_f, cap, floor, state, o_out, H, d, dv):
+        """o_out float32 [T, H dv]: the read-outs of a matrix memory with exponential gates, token by token, from the
+        stacked projection q | k | v | output gate | i | f (float32); state float32 [slots, H d dv + H d + H]."""
+        self._check(self.lib.srlm_matrix_memory_recurrence(
+            _ptr(proj), C.c_longlong(proj.stride(0)), _ptr(bias_i), _ptr(bias_f), C.c_float(cap), C.c_float(floor),
+            _ptr(state), C.c_longlong(state.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.slots), _ptr(o_out),
+            C.c_int(ctx.n_entries), C.c_int(H), C.c_int(d), C.c_int(dv), _stream()), "matrix_memory_recurrence")
+
+    def matrix_memory_output(self, o, norm_w, eps, proj, g_off, out, H, dv):
+        """out [T, H dv] = per head o / sqrt(mean(o^2) + eps), times norm_w (float32 [H dv]), times the logistic of the
+        columns g_off .. of proj."""
+        self._check(self.lib.srlm_matrix_memory_output(
+            _ptr(o), _ptr(norm_w), C.c_float(eps), _ptr(proj), C.c_longlong(proj.stride(0)), C.c_int(g_off), _ptr(out),
+            dtype_code(out.dtype), C.c_int(o.shape[0]), C.c_int(H), C.c_int(dv), _stream()), "matrix_memory_output")
+
+    # ---- the gated linear recurrence --------------------------------------------------------------------
+    def recurrence_gates(self, u, Ra, Ri, ba, bi, rate, a_out, b_out, blocks):
+        """a_out = exp(-rate * logistic(Ra u + ba)), b_out = sqrt(1 - a^2) * logistic(Ri u + bi) * u; u float32 [T, C];
+        Ra, Ri [blocks, C / blocks, C / blocks] (block-diagonal, [out, in])."""
+        T, Cn = u.shape
+        self._check(self.lib.srlm_recurrence_gates(_ptr(u), _ptr(Ra), _ptr(Ri), dtype_code(Ra.dtype), _ptr(ba), _ptr(bi),
+                                                   _ptr(rate), _ptr(a_out), _ptr(b_out), C.c_int(T), C.c_int(Cn),
+                                                   C.c_int(blocks), _stream()), "recurrence_gates")
+
+    def linear_recurrence(self, ctx, a, b, y, y_column, y_bias, state, out):
+        """S <- a S + b per channel and token, from the slots' S (the first C floats of a row of ``state``), renewed at
+        the end; out [T, C] = S * gelu_tanh(y[:, y_column : + C] + y_bias)."""
+        T, Cn = a.shape
+        ptr, ld = self._columns(y, y_column, Cn)
+        self._check(self.lib.srlm_linear_recurrence(_ptr(a), _ptr(b), ptr, ld, _ptr(y_bias), _ptr(state),
+                                                    C.c_longlong(state.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.slots),
+                                                    _ptr(out), dtype_code(out.dtype), C.c_int(ctx.n_entries), C.c_int(Cn),
+                                                    _stream()), "linear_recurrence")
+
     # ---- attention over a cached latent ----------------------------------------------------
     def latent_append(self, proj, c_off, norm_w, eps, rotation, cache, kv_slot, rank, rot):
         """cache row of each token = [rms_norm(proj[c_off : c_off + rank]) * norm_w | rotated proj[.. + rot]]."""
@@ -1094,7 +1217,8 @@ class KernelLibrary:
         self._check(self.lib.srlm_latent_append(
             _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), C.c_int(c_off), _ptr(norm_w),
             C.c_float(eps), _ptr(rotation.cos if pairs else None), _ptr(rotation.sin if pairs else None),
-            C.c_int(pairs), _ptr(cache), dtype_code(cache.dtype), _ptr(kv_slot), C.c_int(proj.shape[0]),
+            C.c_int(pairs), C.c_int(int(bool(pairs and not rotation.interleaved))), _ptr(cache), dtype_code(cache.dtype),
+            _ptr(kv_slot), C.c_int(proj.shape[0]),
             C.c_int(rank), C.c_int(rot), _stream()), "latent_append")
 
     def latent_absorb(self, proj, uk, rotation, q_out, heads, dim, rot, rank):
@@ -1102,7 +1226,8 @@ class KernelLibrary:
         pairs = rotation.pairs if rotation is not None else 0
         self._check(self.lib.srlm_latent_absorb(
             _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), _ptr(uk), dtype_code(uk.dtype),
-            _ptr(rotation.cos if pairs else None), _ptr(rotation.sin if pairs else None), C.c_int(pairs), _ptr(q_out),
+            _ptr(rotation.cos if pairs else None), _ptr(rotation.sin if pairs else None), C.c_int(pairs),
+            C.c_int(int(bool(pairs and not rotation.interleaved))), _ptr(q_out),
             C.c_int(proj.shape[0]), C.c_int(heads), C.c_int(dim), C.c_int(rot), C.c_int(rank), _stream()),
             "latent_absorb")
 
@@ -1130,8 +1255,8 @@ class KernelLibrary:
         pairs = rotation.pairs if rotation is not None else 0
         self._check(self.lib.srlm_latent_rotate_q(
             _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), _ptr(rotation.cos if pairs else None),
-            _ptr(rotation.sin if pairs else None), C.c_int(pairs), _ptr(q_out), C.c_int(proj.shape[0]), C.c_int(heads),
-            C.c_int(dim), C.c_int(rot), _stream()), "latent_rotate_q")
+            _ptr(rotation.sin if pairs else None), C.c_int(pairs), C.c_int(int(bool(pairs and not rotation.interleaved))),
+            _ptr(q_out), C.c_int(proj.shape[0]), C.c_int(heads), C.c_int(dim), C.c_int(rot), _stream()), "latent_rotate_q")
 
     def latent_prefill_attention(self, ctx, q, pages, kv_rows, cu_kv, out, block_table, heads, dim, rot, dv, rank,
                                  v_off, scale):

@@ -3,6 +3,7 @@
 ``pre_norm``: r = x + mixer(norm(x)); x' = r + ff(norm(r))  (src/model/native.rs:526-562).
 ``sandwich_gated``: a norm before and after each sublayer and a learned gate on its result (see the class).
 ``parallel``: h = norm(x); x' = x + mixer(h) + ff(h): one norm, both sublayers read it.
+``post_norm``: x' = norm(a x + mixer(x)), then x'' = norm(a x' + ff(x')): the norm comes after the sum.
 
 The residual stream is a float32 tensor updated in place.  A block does not add
 its feed-forward output itself: it returns it as *pending*, and the next norm
@@ -11,6 +12,8 @@ its feed-forward output itself: it returns it as *pending*, and the next norm
 from __future__ import annotations
 
 from typing import List
+
+import torch
 
 from ..config.spec import LayerSpec, RunStep
 from ..kernels import ops
@@ -205,3 +208,58 @@ class SandwichGatedBlock(Block):
         gate = self.ff_gate(ctx, n, "block.gate")
         self._join(ctx, residual, h, gate, self.ff_gate_bias, self.ff_post_norm, after, n)
         return handed
+
+
+@register_block("post_norm")
+class PostNormBlock(Block):
+    """The norm comes after the sum, and the stream itself is what gets normed:
+
+        x <- norm_1(a x + mixer(x));   x <- norm_2(a x + ff(x))        a = ``residual_scale``
+
+    The sublayers read the stream as it is (in the activation dtype).  One kernel per sublayer scales, adds, norms,
+    rewrites the float32 stream and leaves the activation-dtype copy that the next sublayer's products read
+    (ops.postnorm_scale_add), so nothing is left pending behind a block of this kind: a block of this kind behind it is
+    handed that copy as its input (a NormedInput without partial sums); any other block norms the stream itself."""
+
+    def __init__(self, spec: LayerSpec, tensors: dict, mctx):
+        p = spec.weight_prefix
+        self.spec = spec
+        norm = lambda ns, name: lookup(NORMS, ns.kind, "norm")(ns, p + name, tensors, mctx)
+        self.mixer_norm = norm(spec.mixer_norm, spec.mixer_norm_name)
+        self.mixer = lookup(MIXERS, spec.mixer.kind, "mixer")(spec.mixer, p, tensors, mctx)
+        self.ff_norm = self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.ff_norm = norm(spec.feed_forward_norm, spec.feed_forward_norm_name)
+            self.feed_forward = lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward")(
+                spec.feed_forward, p, tensors, mctx)
+        self.hidden = spec.mixer_norm.size
+        self.alpha = float(spec.residual_scale)
+        self.replayable = all(getattr(part, "replayable", True) for part in (self.mixer, self.feed_forward))
+
+    @classmethod
+    def tensor_decls(cls, spec: LayerSpec, prefix: str = "") -> List[TensorDecl]:
+        return PreNormBlock.tensor_decls(spec, prefix)       # the same parts under the same names
+
+    def _join(self, residual, sub, norm, copy):
+        ops.postnorm_scale_add(residual, sub, norm.weight, self.alpha, norm.spec.eps, norm.spec.unit_offset, copy)
+
+    def forward(self, ctx, residual, pending, run_step: RunStep, next_block=None):
+        T = residual.shape[0]
+        low = ctx.dtype != torch.float32
+        # the sublayers' input: the stream itself in float32, its copy in the activation dtype otherwise
+        x = ctx.workspace.get("block.normed", T, self.hidden, ctx.dtype) if low else residual
+        if isinstance(pending, NormedInput):
+            assert pending.ss_parts is None and pending.xw.data_ptr() == x.data_ptr(), \
+                "only a block of this kind hands this block a prepared input"
+        else:
+            if pending is not None:
+                ops.residual_add(residual, pending)
+            if low:
+                ops.cast(residual, x)
+        mixed = self.mixer.forward(ctx, x, run_step)
+        self._join(residual, mixed, self.mixer_norm, x if low else None)
+        if self.feed_forward is not None:
+            self._join(residual, self.feed_forward.forward(ctx, x), self.ff_norm, x if low else None)
+        if isinstance(next_block, PostNormBlock):
+            return NormedInput(x, None, self.hidden, 0.0)
+        return None

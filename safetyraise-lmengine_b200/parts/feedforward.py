@@ -61,3 +61,29 @@ class GatedDense(Part):
             gu = self.gate_up(ctx, x, "ffn.gate_up")
             ops.swiglu(gu, h)
         return self.down(ctx, h, "ffn.down")
+
+
+@register_feed_forward("dense")
+class Dense(Part):
+    """down(act(up(x))) without a gate; ``activation`` "gelu": the exact one.  The first product writes float32 and the
+    activation rounds once, into the second product's input."""
+
+    def __init__(self, spec, prefix: str, tensors: dict, mctx):
+        if spec.activation != "gelu":
+            raise Unsupported(f"a dense feed-forward with activation {spec.activation!r} is not implemented")
+        self.spec = spec
+        nm = spec.dense_names
+        self.up = Linear(tensors[prefix + nm.up], prefix + nm.up)
+        self.down = Linear(tensors[prefix + nm.down], prefix + nm.down)
+
+    @classmethod
+    def tensor_decls(cls, spec, prefix: str) -> List[TensorDecl]:
+        nm = spec.dense_names
+        return [TensorDecl(prefix + nm.up, (spec.intermediate_size, spec.hidden_size), MATRIX),
+                TensorDecl(prefix + nm.down, (spec.hidden_size, spec.intermediate_size), MATRIX)]
+
+    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+        z = self.up(ctx, x, "dense.z", out_dtype=torch.float32)
+        h = ctx.workspace.get("dense.h", x.shape[0], self.spec.intermediate_size, ctx.dtype)
+        ops.activation(z, h, self.spec.activation)
+        return self.down(ctx, h, "dense.down")

@@ -5,8 +5,12 @@ rotated key part (rot_dim elements) that all heads share.  Head h's unrotated ke
 value U_v,h c; the score of query i on key j is (q_i . U_k,h c_j + qr_i . kr_j) * scale.  Neither keys
 nor values are formed: the up projection of the keys is folded into the query (U_k,h^T q_i), the
 attention runs over [c | kr] with the values being c itself, and the up projection of the values is
-applied to the attended latent.  Each head's output is multiplied by the sigmoid of a projection of
-the mixer's input before the output projection.
+applied to the attended latent.  With ``output_gate`` each head's output is multiplied by the sigmoid of a
+projection of the mixer's input before the output projection.  With ``q_rank`` the queries pass a latent of their
+own: q = W_uq N(w, W_dq h).  With ``window`` a query sees itself and the window - 1 tokens before it, and the
+pages behind the widest window of the entry's readers go back to the pool.  A mixer without a down projection
+(``own_kv`` False) reads the latent and the rotated key part that the run step whose cache entry it names
+cached, with up projections, queries and window of its own.
 
 Prompts in bfloat16 (steps with an entry of more than four tokens) take the other road when the sizes
 fit the tensor-core kernel: the latents of the entries' whole contexts are gathered from the pages, one
@@ -22,9 +26,9 @@ from typing import List
 
 import torch
 
-from ..cache.manager import PAGED_ALL
+from ..cache.manager import PAGED_ALL, PAGED_WINDOW
 from ..config.spec import LatentAttentionSpec, RunStep
-from ..errors import Unsupported
+from ..errors import ConfigError, Unsupported
 from ..kernels import ops
 from ..weights.loader import MATRIX, VECTOR, TensorDecl
 from .base import POSITION_ENCODINGS, ROTATION, CacheNeed, Part, lookup, register_mixer
@@ -36,11 +40,22 @@ class LatentAttention(Part):
     def __init__(self, spec: LatentAttentionSpec, prefix: str, tensors: dict, mctx):
         self.spec = s = spec
         p, nm = prefix, spec.names
-        rows = [tensors[p + nm.q], tensors[p + nm.down]] + ([tensors[p + nm.gate]] if s.output_gate else [])
+        # one product for everything that reads the mixer's input: the queries (or their latent), the down projection
+        # (layers that cache a latent of their own), the gate; float32 result
+        q_rows = s.q_rank if s.q_rank else s.heads * (s.head_dim + s.rot_dim)
+        rows = [tensors[p + (nm.q_down if s.q_rank else nm.q)]]
+        if s.own_kv:
+            rows.append(tensors[p + nm.down])
+        if s.output_gate:
+            rows.append(tensors[p + nm.gate])
         self.proj = Linear(torch.cat(rows, dim=0).contiguous(), p + "q_down_gate")
-        self.c_off = s.heads * (s.head_dim + s.rot_dim)
-        self.g_off = self.c_off + s.kv_rank + s.rot_dim if s.output_gate else -1
-        self.latent_norm_w = tensors[p + nm.latent_norm]
+        self.c_off = q_rows
+        self.g_off = q_rows + (s.kv_rank + s.rot_dim if s.own_kv else 0) if s.output_gate else -1
+        self.q_norm_w = self.q_up = None
+        if s.q_rank:
+            self.q_norm_w = tensors[p + nm.q_norm]
+            self.q_up = Linear(tensors[p + nm.q_up], p + nm.q_up)
+        self.latent_norm_w = tensors[p + nm.latent_norm] if s.own_kv else None
         self.uk = tensors[p + nm.up_k].view(s.heads, s.head_dim, s.kv_rank).contiguous()
         # per head [kv_rank, v_head_dim]: a thread of the expanding kernel owns one output column
         self.uv_t = tensors[p + nm.up_v].view(s.heads, s.v_head_dim, s.kv_rank).transpose(1, 2).contiguous()
@@ -58,11 +73,18 @@ class LatentAttention(Part):
     @classmethod
     def tensor_decls(cls, s: LatentAttentionSpec, prefix: str) -> List[TensorDecl]:
         p, nm = prefix, s.names
-        decls = [TensorDecl(p + nm.q, (s.heads * (s.head_dim + s.rot_dim), s.hidden_size), MATRIX),
-                 TensorDecl(p + nm.down, (s.kv_rank + s.rot_dim, s.hidden_size), MATRIX),
-                 TensorDecl(p + nm.latent_norm, (s.kv_rank,), VECTOR),
-                 TensorDecl(p + nm.up_k, (s.heads * s.head_dim, s.kv_rank), MATRIX),
-                 TensorDecl(p + nm.up_v, (s.heads * s.v_head_dim, s.kv_rank), MATRIX)]
+        hd = s.heads * (s.head_dim + s.rot_dim)
+        if s.q_rank:
+            decls = [TensorDecl(p + nm.q_down, (s.q_rank, s.hidden_size), MATRIX),
+                     TensorDecl(p + nm.q_norm, (s.q_rank,), VECTOR),
+                     TensorDecl(p + nm.q_up, (hd, s.q_rank), MATRIX)]
+        else:
+            decls = [TensorDecl(p + nm.q, (hd, s.hidden_size), MATRIX)]
+        if s.own_kv:
+            decls += [TensorDecl(p + nm.down, (s.kv_rank + s.rot_dim, s.hidden_size), MATRIX),
+                      TensorDecl(p + nm.latent_norm, (s.kv_rank,), VECTOR)]
+        decls += [TensorDecl(p + nm.up_k, (s.heads * s.head_dim, s.kv_rank), MATRIX),
+                  TensorDecl(p + nm.up_v, (s.heads * s.v_head_dim, s.kv_rank), MATRIX)]
         if s.output_gate:
             decls.append(TensorDecl(p + nm.gate, (s.heads, s.hidden_size), MATRIX))
         decls.append(TensorDecl(p + nm.o, (s.hidden_size, s.heads * s.v_head_dim), MATRIX))
@@ -71,30 +93,38 @@ class LatentAttention(Part):
     @classmethod
     def cache_need_of(cls, s: LatentAttentionSpec) -> CacheNeed:
         # one KV head of kv_rank + rot_dim elements per token, and no value pool: the values are the latent
-        return CacheNeed(PAGED_ALL, 1, s.kv_rank + s.rot_dim, None, v_head_dim=0)
+        if s.window and s.cache_window and s.cache_window < s.window:
+            raise ConfigError("a latent attention's cache keeps fewer keys than its window sees")
+        keeps = s.cache_window if s.window else None
+        return CacheNeed(PAGED_WINDOW if keeps else PAGED_ALL, 1, s.kv_rank + s.rot_dim, keeps, v_head_dim=0)
 
     def forward(self, ctx, x: torch.Tensor, run_step: RunStep) -> torch.Tensor:
         s = self.spec
         T = x.shape[0]
+        if run_step.writes_cache != s.own_kv:
+            raise ConfigError("a latent attention writes its cache entry exactly when it has a down projection of its own")
         proj = self.proj(ctx, x, "latent.proj", out_dtype=torch.float32)
         cache, _, group = ctx.cache.kv_of_entry(run_step.cache)
         rot = self.position.rotation(ctx) if self.position is not None else None
-        if rot is not None and not rot.interleaved:
-            raise Unsupported("the latent attention kernels rotate interleaved pairs only")
-        if run_step.writes_cache:
+        if s.own_kv:
             ops.latent_append(proj, self.c_off, self.latent_norm_w, s.latent_norm_eps, rot, cache, ctx.kv_slot[group],
                               s.kv_rank, s.rot_dim)
+        q_heads = proj                 # heads x [dim | rot_dim] lead the row
+        if s.q_rank:
+            cq = ctx.workspace.get("latent.cq", T, s.q_rank, ctx.dtype)
+            ops.rmsnorm_columns(proj, 0, s.q_rank, self.q_norm_w, s.latent_norm_eps, cq)
+            q_heads = self.q_up(ctx, cq, "latent.q_heads_raw", out_dtype=torch.float32)
         gated = ctx.workspace.get("latent.out", T, s.heads * s.v_head_dim, ctx.dtype)
-        if (self.up_kv is not None and ctx.max_q_len > 4 and run_step.writes_cache
+        if (self.up_kv is not None and ctx.max_q_len > 4 and s.own_kv and not s.window and s.output_gate and not s.q_rank
                 and ops.latent_prompt_takes(s.head_dim, s.rot_dim, s.v_head_dim, s.kv_rank)):
             self._attend_in_head_space(ctx, proj, cache, group, rot, gated)
             return self.out(ctx, gated, "latent.proj_out")
         qd = s.kv_rank + s.rot_dim
         q = ctx.workspace.get("latent.q", T, s.heads * qd, torch.float32)
-        ops.latent_absorb(proj, self.uk, rot, q, s.heads, s.head_dim, s.rot_dim, s.kv_rank)
+        ops.latent_absorb(q_heads, self.uk, rot, q, s.heads, s.head_dim, s.rot_dim, s.kv_rank)
         o_lat = ctx.workspace.get("latent.o", T, s.heads * s.kv_rank, torch.float32)
         ops.paged_attention_general(ctx, q, cache, None, o_lat, ctx.block_tables[group], None, s.heads, 1, qd,
-                                    s.kv_rank, s.softmax_scale)
+                                    s.kv_rank, s.softmax_scale, s.window or 0)
         ops.latent_expand(o_lat, self.uv_t, proj, self.g_off, gated, s.heads, s.kv_rank, s.v_head_dim)
         return self.out(ctx, gated, "latent.proj_out")
 

@@ -11,6 +11,11 @@ experts have no biases, so W (w h) = w (W h), and the first grouped product mult
 the pair's weight ahead of the activation (steps of many tokens, whose rows are gathered into tiles, scale the
 gathered rows).
 
+``gated`` False: an expert (and the shared one) is W_down act(W_up h) with ``activation`` "gelu" (the exact one).
+``scoring`` "softmax_over_all": the scores are the softmax over all experts' logits, the choice may be limited to the
+best ``groups_kept`` of ``groups`` equal groups of neighbouring experts (a group counts as its largest score), and the
+weights are the chosen scores over their sum.
+
 The pairs (token, chosen expert) are ordered by expert on the device and every expert's rows run through
 one grouped product per projection; a token's result does not depend on what else is in the step, and
 nothing is planned on the host, so decode steps replay from CUDA graphs.
@@ -32,13 +37,19 @@ from .linear import Linear
 @register_feed_forward("routed_experts")
 class RoutedExperts(Part):
     def __init__(self, spec: RoutedExpertsSpec, prefix: str, tensors: dict, mctx):
-        if spec.activation not in ("clamped_glu", "silu"):
+        if spec.activation not in (("clamped_glu", "silu") if spec.gated else ("gelu",)):
             raise Unsupported(f"routed experts with activation {spec.activation!r} are not implemented")
+        if not spec.gated and spec.weight_on_input:
+            raise Unsupported("a weight on an expert's input comes with gated experts only")
         if spec.scoring not in ops.ROUTER_SCORING:
             raise Unsupported(f"routed experts with router scoring {spec.scoring!r} are not implemented")
         if spec.activation == "silu" and spec.shared_size:
             raise Unsupported("an expert that every token runs comes with the clamped activation only")
         self.spec = spec
+        self.groups = (spec.groups, spec.groups_kept)
+        if not spec.gated:
+            self._init_plain(spec, prefix, tensors, mctx)
+            return
         self.limit = spec.limit if spec.activation == "clamped_glu" else 0.0      # 0: the plain gated activation
         p, nm = prefix, spec.expert_names
         self.router_bias = tensors[p + nm.router_bias] if spec.router_bias else None
@@ -65,6 +76,24 @@ class RoutedExperts(Part):
         self.first = Linear(torch.cat(first, dim=0).contiguous(), p + "shared_gate_up_router")
         self.router_column = 2 * spec.shared_size
 
+    def _init_plain(self, spec, prefix, tensors, mctx):
+        """Experts without a gate: [experts, ff, hidden] and [experts, hidden, ff]; the first product of the layer's input
+        stacks the shared expert's up rows and the router's rows (float32 result)."""
+        p, nm = prefix, spec.expert_names
+        each = lambda part: [tensors[p + nm.expert.format(e) + part] for e in range(spec.experts)]
+        self.router_bias = tensors[p + nm.router_bias] if spec.router_bias else None
+        self.interleaved = False
+        self.limit = 0.0
+        self.gate_up = torch.stack(each(nm.up)).contiguous()
+        self.down = torch.stack(each(nm.down)).contiguous()
+        first, self.shared_down = [tensors[p + nm.router]], None
+        if spec.shared_size:
+            sp = p + nm.shared
+            first = [tensors[sp + nm.up]] + first
+            self.shared_down = Linear(tensors[sp + nm.down], sp + nm.down)
+        self.first = Linear(torch.cat(first, dim=0).contiguous(), p + "shared_up_router")
+        self.router_column = spec.shared_size
+
     @classmethod
     def tensor_decls(cls, s: RoutedExpertsSpec, prefix: str) -> List[TensorDecl]:
         p, nm = prefix, s.expert_names
@@ -72,16 +101,18 @@ class RoutedExperts(Part):
         decls = []
         for e in range(s.experts):
             ep = p + nm.expert.format(e)
-            decls += [TensorDecl(ep + nm.gate, (s.intermediate_size, H), MATRIX),
-                      TensorDecl(ep + nm.up, (s.intermediate_size, H), MATRIX),
+            if s.gated:
+                decls.append(TensorDecl(ep + nm.gate, (s.intermediate_size, H), MATRIX))
+            decls += [TensorDecl(ep + nm.up, (s.intermediate_size, H), MATRIX),
                       TensorDecl(ep + nm.down, (H, s.intermediate_size), MATRIX)]
         decls.append(TensorDecl(p + nm.router, (s.experts, H), MATRIX))
         if s.router_bias:
             decls.append(TensorDecl(p + nm.router_bias, (s.experts,), VECTOR))
         if s.shared_size:
             sp = p + nm.shared
-            decls += [TensorDecl(sp + nm.gate, (s.shared_size, H), MATRIX), TensorDecl(sp + nm.up, (s.shared_size, H), MATRIX),
-                      TensorDecl(sp + nm.down, (H, s.shared_size), MATRIX)]
+            if s.gated:
+                decls.append(TensorDecl(sp + nm.gate, (s.shared_size, H), MATRIX))
+            decls += [TensorDecl(sp + nm.up, (s.shared_size, H), MATRIX), TensorDecl(sp + nm.down, (H, s.shared_size), MATRIX)]
         return decls
 
     takes_addend = True       # forward(..., add=...) adds a tensor of the output's shape and dtype in the combination
@@ -102,7 +133,7 @@ class RoutedExperts(Part):
         if (self.interleaved and ops.grouped_products_in_tensor_memory and pairs >= 64 * s.experts
                 and s.intermediate_size % 8 == 0):
             ops.moe_route(first, self.router_bias, s.top, choice, weight, column=self.router_column, experts=s.experts,
-                          scoring=s.scoring)
+                          scoring=s.scoring, groups=self.groups)
             return self._forward_tiles(ctx, x, first, choice, weight, add)
         heads = ws.get("moe.heads", 2, s.experts + 1, torch.int32, reserve=2)
         order = ws.get("moe.order", 2 * T, s.top, torch.int32, reserve=2 * ws.max_tokens)
@@ -110,14 +141,18 @@ class RoutedExperts(Part):
         pair_of_row, row_of_pair = order[:T].view(-1), order[T:].view(-1)
         if ops.moe_sort_routes(T, s.experts):          # a small step: the block that orders the pairs routes them too
             ops.moe_sort(choice, s.experts, offsets, tiles, pair_of_row, row_of_pair,
-                         route=(first, self.router_column, self.router_bias, weight), scoring=s.scoring)
+                         route=(first, self.router_column, self.router_bias, weight), scoring=s.scoring,
+                         groups=self.groups)
         else:
             ops.moe_route(first, self.router_bias, s.top, choice, weight, column=self.router_column, experts=s.experts,
-                          scoring=s.scoring)
+                          scoring=s.scoring, groups=self.groups)
             ops.moe_sort(choice, s.experts, offsets, tiles, pair_of_row, row_of_pair)
         y = ws.get("moe.y", pairs, s.intermediate_size, ctx.dtype, reserve=ws.max_tokens * s.top)
-        ops.moe_grouped(x, pair_of_row, s.top, self.gate_up, y, offsets, tiles, glu=True, interleaved=self.interleaved,
-                        limit=self.limit, alpha=s.glu_alpha, pair_scale=weight if s.weight_on_input else None)
+        if s.gated:
+            ops.moe_grouped(x, pair_of_row, s.top, self.gate_up, y, offsets, tiles, glu=True, interleaved=self.interleaved,
+                            limit=self.limit, alpha=s.glu_alpha, pair_scale=weight if s.weight_on_input else None)
+        else:
+            ops.moe_grouped(x, pair_of_row, s.top, self.gate_up, y, offsets, tiles, act=s.activation)
         rows = ws.get("moe.rows", pairs, H, torch.float32, reserve=ws.max_tokens * s.top)
         ops.moe_grouped(y, None, 1, self.down, rows, offsets, tiles)
         out = ws.get("moe.out", T, H, ctx.dtype)
@@ -131,7 +166,10 @@ class RoutedExperts(Part):
             return None
         s = self.spec
         ys = ctx.workspace.get("moe.shared_y", first.shape[0], s.shared_size, ctx.dtype)
-        ops.clamped_glu(first, ys, s.shared_limit, s.glu_alpha)
+        if s.gated:
+            ops.clamped_glu(first, ys, s.shared_limit, s.glu_alpha)
+        else:
+            ops.activation(first, ys, s.activation)
         return self.shared_down(ctx, ys, "moe.shared_out")
 
     def _forward_tiles(self, ctx, x, first, choice, weight, add=None):

@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--shape 8b|14b|32b] [--workload decode|mixed]
-    python bench.py --design nekedra|tonanex|pabalorn [--design-size 2048|4096]
+    python bench.py --design nekedra|tonanex|pabalorn|dovorax [--design-size 2048|4096]
 
 A "step" is one decode step: every request of the batch gets its next token.
 The default run has the sizes of the 8B configuration (36 layers, hidden 4096,
@@ -39,7 +39,10 @@ eager step spends its time in (``run_design``).
 ``--design tonanex`` does the same for Tonanex stacks with a dense feed-forward
 and with routed experts, ``--design pabalorn`` for Pabalorn stacks of attention
 layers, of layers with an attention and a selective scan side by side, and of
-both in turn, beside Qwen3 and the Tonanex stack with routed experts.
+both in turn, beside Qwen3 and the Tonanex stack with routed experts,
+``--design dovorax`` for Dovorax stacks of each of its three layer kinds and of
+all of them, beside Qwen3, Nekedra's latent attention and delta rule, and the
+Tonanex stack with routed experts.
 """
 from __future__ import annotations
 
@@ -604,6 +607,35 @@ def pabalorn_config(size: dict, kinds) -> dict:
             "layers": [{"type": k, "mixer": mixers[k], "mlp": mlp} for k in kinds]}
 
 
+DOVORAX_WINDOW = 1024
+
+
+def dovorax_config(size: dict, kinds) -> dict:
+    """A Dovorax configuration whose layers have the sizes of a Qwen3 layer of the same width: a latent attention with
+    heads of 128 + 64, a latent of 512, a query latent of three quarters of a width and a window of 1,024 tokens; a
+    'parallel' layer of attention with heads of 128 behind convolutions of 4 taps beside a matrix memory of half as
+    many heads of 128 x 128; a gated linear recurrence of one width in blocks of 128 channels, 4 taps; the first
+    layer's feed-forward dense (three widths), the others' 16 ungated experts of three quarters of a width in 4 groups
+    of which 2 are kept, 4 a token, plus a shared one of one width and a half."""
+    W, H, G = size["width"], size["heads"], size["kv_heads"]
+    scaling = {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+    mixers = {
+        "latent_attention": {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 3 * W // 4,
+                             "scale": 192 ** -0.5, "mask": {"size": DOVORAX_WINDOW},
+                             "rot": {"base": 10000.0, "dims": 64, "scaling": scaling}},
+        "parallel": {"left": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "conv": 4, "scale": 128 ** -0.5,
+                              "rot": {"base": 10000.0, "dims": 64, "scaling": scaling}},
+                     "right": {"heads": H // 2, "dim": 128, "vdim": 128, "gate_cap": 15.0},
+                     "left_scale": 0.7, "right_scale": 0.7},
+        "rglru": {"width": W, "blocks": W // 128, "conv": 4},
+    }
+    moe = {"kind": "moe", "expert": {"ff": 3 * W // 4}, "shared": {"ff": 3 * W // 2},
+           "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    return {"architecture": "Dovorax", "width": W, "vocab": DESIGN_VOCAB, "norm": {"eps": 1e-6}, "postln_alpha": 2.0,
+            "layers": [{"type": k, "mixer": mixers[k], "mlp": {"kind": "dense", "ff": 3 * W} if i == 0 else moe}
+                       for i, k in enumerate(kinds)]}
+
+
 def qwen3_config(size: dict) -> dict:
     return dict(BASE, num_hidden_layers=DESIGN_LAYERS, hidden_size=size["width"], num_attention_heads=size["heads"],
                 num_key_value_heads=size["kv_heads"], intermediate_size=3 * size["width"], vocab_size=DESIGN_VOCAB)
@@ -628,13 +660,25 @@ def run_design(args) -> dict:
                   "pabalorn attention": ["attention"] * DESIGN_LAYERS, "pabalorn parallel": ["parallel"] * DESIGN_LAYERS,
                   "pabalorn mixed": ["attention", "parallel"] * (DESIGN_LAYERS // 2)}
         make = lambda size, kinds: (tonanex_config if kinds[0] == "moe" else pabalorn_config)(size, kinds)
+    if args.design == "dovorax":
+        stacks = {"qwen3": None, "nekedra latent": ["latent_attention"] * DESIGN_LAYERS, "nekedra delta": ["delta"] * DESIGN_LAYERS,
+                  "tonanex experts": ["moe"] * DESIGN_LAYERS,
+                  "dovorax latent": ["latent_attention"] * DESIGN_LAYERS, "dovorax parallel": ["parallel"] * DESIGN_LAYERS,
+                  "dovorax recurrence": ["rglru"] * DESIGN_LAYERS,
+                  "dovorax mixed": ["latent_attention", "parallel", "rglru", "latent_attention"]}
+        make = lambda size, kinds: (tonanex_config if kinds[0] == "moe" else nekedra_config if kinds[0] == "delta" else None)(size, kinds)
     out = {"metric": args.design + "_beside_qwen3", "layers": DESIGN_LAYERS, "prefill_tokens": PREFILL_TOKENS,
            "decode_batch": batch, "decode_context": context, "dtype": "bf16", "data": "synthetic", "sizes": {}}
     sizes = [args.design_size] if args.design_size else sorted(DESIGN_SIZES)
     for name in sizes:
         size, rows = DESIGN_SIZES[name], {}
         for label, kinds in stacks.items():
-            cfg = qwen3_config(size) if kinds is None else make(size, kinds)
+            if label.startswith("dovorax"):
+                cfg = dovorax_config(size, kinds)
+            elif label.startswith("nekedra"):
+                cfg = nekedra_config(size, kinds)
+            else:
+                cfg = qwen3_config(size) if kinds is None else make(size, kinds)
             eng = build_engine(cfg, DESIGN_LAYERS, batch + 1, batch * (context + MAX_GROWTH) + PREFILL_TOKENS,
                                PREFILL_TOKENS)
             randomize_cache(eng)
@@ -673,8 +717,8 @@ def main() -> int:
     ap.add_argument("--only-prefill", action="store_true", help="run just the 2,048-token prefill (for profilers)")
     ap.add_argument("--streaming-kernel", action="store_true",
                     help="steps of up to 8 tokens on the weight-streaming mma.sync kernel instead of the tensor-core one")
-    ap.add_argument("--design", default=None, choices=["nekedra", "tonanex", "pabalorn"],
-                    help="instead of the default workload: prefill and decode of Nekedra, Tonanex or Pabalorn stacks "
+    ap.add_argument("--design", default=None, choices=["nekedra", "tonanex", "pabalorn", "dovorax"],
+                    help="instead of the default workload: prefill and decode of Nekedra, Tonanex, Pabalorn or Dovorax stacks "
                          "beside the Qwen3 decoder at equal layer sizes")
     ap.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES), help="one width of --design")
     ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,

@@ -47,6 +47,13 @@ def _num(d: dict, key: str, where: str) -> float:
     return float(v)
 
 
+def _real(d: dict, key: str, where: str) -> float:
+    v = d.get(key)
+    if isinstance(v, bool) or not isinstance(v, (int, float)) or not math.isfinite(v):
+        raise ConfigError(f"config.json: {where}{key!r} must be a finite number, got {v!r}")
+    return float(v)
+
+
 def _obj(d: dict, key: str, where: str) -> dict:
     v = d.get(key)
     if not isinstance(v, dict):
@@ -141,7 +148,7 @@ def read_spec(root: dict) -> ModelSpec:
         raise ConfigError(f"config.json: architecture {root.get('architecture')!r} is not {ARCHITECTURE}")
     width, vocab = _int(root, "width", ""), _int(root, "vocab", "")
     eps = _num(_obj(root, "norm", ""), "eps", "norm.")
-    alpha = _num(root, "postln_alpha", "")
+    alpha = _real(root, "postln_alpha", "")
     entries = root.get("layers")
     if not isinstance(entries, list) or not entries or len(entries) > MAX_LAYERS:
         raise ConfigError(f"config.json: 'layers' must list 1 to {MAX_LAYERS} layers")
@@ -160,7 +167,7 @@ def read_spec(root: dict) -> ModelSpec:
             right = _matrix_memory(_obj(m, "right", w), width, eps, w + "right.", "mix.right.")
             mixers.append(SideBySideSpec(kind="side_by_side", hidden_size=width, mixers=(left, right),
                                          combine="weighted_sum",
-                                         weights=(_num(m, "left_scale", w), _num(m, "right_scale", w))))
+                                         weights=(_real(m, "left_scale", w), _real(m, "right_scale", w))))
         elif entry["type"] == "rglru":
             mixers.append(_recurrence(m, width, w))
         else:

@@ -36,11 +36,7 @@ class ConvAttention(Part):
         parts = (nm.q, nm.k, nm.v)
         self.proj = Linear(torch.cat([tensors[p + n] for n in parts], dim=0).contiguous(), p + "q_k_v")
         self.channels = s.heads * s.head_dim + s.kv_heads * (s.head_dim + s.v_head_dim)
-        self.conv_w = None
-        if s.conv_taps > 1:
-            self.conv_w = torch.cat([tensors[p + n + nm.conv_suffix] for n in parts], dim=0).float().contiguous()
-        else:
-            self.conv_w = torch.ones((self.channels, 1), dtype=torch.float32, device=mctx.device)
+        self.conv_w = torch.cat([tensors[p + n + nm.conv_suffix] for n in parts], dim=0).float().contiguous()
         self.q_norm_w = self.k_norm_w = None
         if s.qk_norm_eps is not None:
             self.q_norm_w, self.k_norm_w = tensors[p + nm.q + nm.norm_suffix], tensors[p + nm.k + nm.norm_suffix]
@@ -60,8 +56,7 @@ class ConvAttention(Part):
         decls = [TensorDecl(p + n, (rows, s.hidden_size), MATRIX) for n, rows in sizes.items()]
         if s.qk_norm_eps is not None:
             decls += [TensorDecl(p + n + nm.norm_suffix, (s.head_dim,), VECTOR) for n in (nm.q, nm.k)]
-        if s.conv_taps > 1:
-            decls += [TensorDecl(p + n + nm.conv_suffix, (rows, s.conv_taps), VECTOR) for n, rows in sizes.items()]
+        decls += [TensorDecl(p + n + nm.conv_suffix, (rows, s.conv_taps), VECTOR) for n, rows in sizes.items()]
         decls.append(TensorDecl(p + nm.o, (s.hidden_size, s.heads * s.v_head_dim), MATRIX))
         return decls
 

@@ -134,7 +134,8 @@ def conv_attention(h, W, p, m, eps):
     q = rms_norm(proj("q").view(T, H, d), W[p + "q.norm"], eps)
     k = rms_norm(proj("k").view(T, G, d), W[p + "k.norm"], eps)
     v = proj("v").view(T, G, dv)
-    q, k = rotate(q, m["rot"]), rotate(k, m["rot"])
+    if m.get("rot"):
+        q, k = rotate(q, m["rot"]), rotate(k, m["rot"])
     k, v = k.repeat_interleave(H // G, dim=1), v.repeat_interleave(H // G, dim=1)
     s = torch.einsum("ihd,jhd->hij", q, k) * m["scale"]
     a = softmax_rows(s, visible(T, None), one_more=True)

@@ -116,7 +116,7 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
   const int first_key = window > 0 ? max(0, min_pos - window + 1) : 0;
   const int kvec = dk / 8, vvec = DVT / 8;
 
-  const size_t row0 = kv_rows ? (size_t)cu_kv[e] : 0;
+  const long long row0 = kv_rows ? (long long)cu_kv[e] : 0;       // where key 0 would lie: negative when the first keys were not gathered
   const int page_width = page_skip + dk - dim_rows;
   auto fetch = [&](int jb, int buf) {
     for (int idx = tid; idx < kMmaKeys * kvec; idx += blockDim.x) {
@@ -125,7 +125,7 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
       const bf16* src = k_cache;
       if (there && kv_rows) {
         if (c * 8 < dim_rows) {
-          src = kv_rows + (row0 + j) * ld_rows + (size_t)kvh * dim_rows + c * 8;
+          src = kv_rows + (size_t)(row0 + j) * ld_rows + (size_t)kvh * dim_rows + c * 8;
         } else {
           const size_t rowi = (size_t)table[j / page_size] * page_size + (j % page_size);
           src = k_cache + rowi * page_width + page_skip + (c * 8 - dim_rows);
@@ -142,7 +142,7 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
         const bool there = j >= first_key && j <= max_pos;     // pages before a window's first key may be given back
         const bf16* src = k_cache;
         if (there && kv_rows) {
-          src = kv_rows + (row0 + j) * ld_rows + v_off + (size_t)kvh * dv + slab * DVT + c * 8;
+          src = kv_rows + (size_t)(row0 + j) * ld_rows + v_off + (size_t)kvh * dv + slab * DVT + c * 8;
         } else if (there) {
           const size_t rowi = ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size);
           src = v_cache + rowi * dv + slab * DVT + c * 8;
@@ -615,6 +615,8 @@ extern "C" int srlm_paged_attention_general_decode(const float* q, const void* k
 // Prompts of an attention over a cached latent, in the heads' own space: q float32 [T, heads, dim + rot];
 // kv_rows bfloat16 [sum of the entries' contexts, ld_rows]: per row the heads' unrotated keys (heads x dim) and,
 // from column v_off, their values (heads x dv); pages: one KV head, rows [latent (rank) | rotated key part (rot)].
+// Row cu_kv[e] + j holds key j of entry e; keys that no row of the step sees (behind the window) need no row, so cu_kv[e]
+// may be negative.  window > 0: a query sees itself and the window - 1 keys before it.
 extern "C" int srlm_latent_prefill_attention_takes(int dim, int rot, int dv, int rank) {
   return dim > 0 && rot >= 0 && dim % 8 == 0 && rot % 8 == 0 && rank % 8 == 0 && (dim + rot) % 16 == 0 && dv % 64 == 0 &&
          srlm_attention_general_mma_takes(dim + rot, dv, 0);
@@ -624,7 +626,7 @@ extern "C" int srlm_latent_prefill_attention(const float* q, const void* pages, 
                                              const int* cu_kv, void* out, int out_dtype, const int* block_table,
                                              int table_stride, const int* cu_q, const int* kv_lens, int n_entries,
                                              int max_q_len, int heads, int dim, int rot, int dv, int rank, int v_off,
-                                             int page_size, float scale, cudaStream_t stream) {
+                                             int page_size, float scale, int window, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return ST_OK;
   if (heads <= 0 || page_size <= 0 || !kv_rows || !cu_kv || !srlm_latent_prefill_attention_takes(dim, rot, dv, rank) ||
       ld_rows % 8 || v_off % 8 || ld_rows < v_off + (long long)heads * dv)
@@ -641,7 +643,7 @@ extern "C" int srlm_latent_prefill_attention(const float* q, const void* pages, 
   const int nbuf = q_bytes + 2 * tile_bytes <= 100 * 1024 ? 2 : 1;
   const size_t smem = q_bytes + nbuf * tile_bytes;
 #define SRLM_LAT_ARGS grid, smem, stream, q, pages, nullptr, out, block_table, table_stride, cu_q, kv_lens, nullptr, heads, \
-                      heads, dk, dv, page_size, scale, 0, nbuf, (const bf16*)kv_rows, ld_rows, cu_kv, dim, v_off, rank
+                      heads, dk, dv, page_size, scale, window, nbuf, (const bf16*)kv_rows, ld_rows, cu_kv, dim, v_off, rank
   if (out_dtype == DT_F32) return slab == 128 ? launch_mma<float, 16>(SRLM_LAT_ARGS) : launch_mma<float, 8>(SRLM_LAT_ARGS);
   if (out_dtype == DT_BF16) return slab == 128 ? launch_mma<bf16, 16>(SRLM_LAT_ARGS) : launch_mma<bf16, 8>(SRLM_LAT_ARGS);
 #undef SRLM_LAT_ARGS

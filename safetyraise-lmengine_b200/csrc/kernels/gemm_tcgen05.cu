@@ -230,6 +230,8 @@ struct GemmArgs {
   // swiglu8 with glu_limit > 0: the output is g * logistic(glu_alpha * g) * (u + 1), g = min(gate, limit),
   // u = clamp(up, -limit, limit), instead of silu(gate) * up
   float glu_limit = 0.f, glu_alpha = 0.f;
+  // persistent kernel, whole tiles, without swiglu8: 1: the output is the exact gelu of the product
+  int act = 0;
 };
 
 __device__ __forceinline__ void cluster_sync_all() {   // every thread of every block of the cluster
@@ -1101,7 +1103,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
         } else {
 #pragma unroll
           for (int j = 0; j < SLAB; ++j) {
-            const float x = __uint_as_float(v[j]);
+            float x = __uint_as_float(v[j]);
+            if (args.act == 1) x = 0.5f * x * (1.f + erff(x * 0.70710678118654752440f));
             const int col = lane_base + lane;
             if (args.c_is_f32) *reinterpret_cast<float*>(sl + j * SLAB_ROW + col * 4) = x;
             else *reinterpret_cast<bf16*>(sl + j * SLAB_ROW + col * 2) = __float2bfloat16_rn(x);
@@ -1640,12 +1643,13 @@ extern "C" int srlm_gemm_tn_tcgen05_static(const void* X, const void* W, void* C
 // negative: the tile is skipped and its rows of C are not written).  W: [groups * N, K], contiguous.  glu: the
 // weight rows of a group come in blocks of 16 (8 gate rows, then the 8 up rows of the same features) and
 // C [M, N / 2] gets g * logistic(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); with
-// limit <= 0 the plain form, gate * logistic(gate) * up.
+// limit <= 0 the plain form, gate * logistic(gate) * up.  act 1 (without glu): C gets the exact gelu of the product.
 extern "C" int srlm_gemm_tn_tcgen05_grouped(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
                                             long long ldx, long long ldc, int groups, const int* group_of_mtile,
-                                            int tile_rows, int glu, float limit, float alpha, int* err_flag,
+                                            int tile_rows, int glu, float limit, float alpha, int act, int* err_flag,
                                             cudaStream_t stream) {
   if (M <= 0) return ST_OK;
+  if (act < 0 || act > 1 || (act && glu)) return refuse(ST_BAD_SIZE, "gemm_tcgen05_grouped: activation %d with glu=%d", act, glu);
   if (tile_rows != 128 && tile_rows != 256) return refuse(ST_BAD_SIZE, "gemm_tcgen05_grouped: tiles of %d rows", tile_rows);
   if (N <= 0 || K <= 0 || groups <= 0 || !group_of_mtile || ldx < K || ldc < (glu ? N / 2 : N) || (glu && N % 16))
     return refuse(ST_BAD_SIZE, "gemm_tcgen05_grouped: M=%d N=%d K=%d groups=%d ldx=%lld ldc=%lld glu=%d", M, N, K, groups, ldx,
@@ -1657,6 +1661,7 @@ extern "C" int srlm_gemm_tn_tcgen05_grouped(const void* X, const void* W, void* 
   a.group_of_mtile = group_of_mtile;
   a.glu_limit = glu && limit > 0.f ? limit : 0.f;
   a.glu_alpha = alpha;
+  a.act = act;
   CUtensorMap mw_copy, mx_copy;
   const CUtensorMap *mw = &mw_copy, *mx = &mx_copy;
   // (the pair form fetches the tokens of a tile in two boxes of 128 rows, one a block)

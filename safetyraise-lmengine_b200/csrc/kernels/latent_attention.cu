@@ -160,21 +160,24 @@ latent_expand_kernel(const float* __restrict__ o_lat, const TW* __restrict__ uv_
 // ---- prompts: per-head keys and values formed for the step ----------------------------------------------
 // A prompt attends in the heads' own space (dim + rot per key, vdim per value: a third of the latent form's
 // arithmetic).  latent_gather copies the latents of every entry's context out of the pages into one
-// contiguous matrix, row cu_kv[e] + j for key j of entry e; one matrix product with [U_k; U_v] then gives all
+// contiguous matrix, row cu_kv[e] + j for key j of entry e (from the first key that the step's windows still see); one matrix product with [U_k; U_v] then gives all
 // heads' unrotated keys and values; the rotated key part stays in the pages and is read from there.
 template <typename TC>
 __global__ void latent_gather_kernel(const TC* __restrict__ cache, TC* __restrict__ dst,
                                      const int* __restrict__ block_table, int table_stride,
-                                     const int* __restrict__ cu_kv, int page_size, int width, int rank) {
+                                     const int* __restrict__ cu_kv, const int* __restrict__ kv_first,
+                                     const int* __restrict__ kv_lens, int page_size, int width, int rank) {
   pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
   pdl_trigger();
+  // keys kv_first[e] .. kv_lens[e] - 1 of entry e go to the rows cu_kv[e] + j (cu_kv[e] is where key 0 would lie)
   const int e = blockIdx.y;
-  const int n = cu_kv[e + 1] - cu_kv[e];
+  const int first = kv_first ? kv_first[e] : 0;
   const int* table = block_table + (size_t)e * table_stride;
-  for (int j = blockIdx.x; j < n; j += gridDim.x) {
-    const size_t row = (size_t)table[j / page_size] * page_size + (j % page_size);
+  for (int j = first + blockIdx.x; j < kv_lens[e]; j += gridDim.x) {
+    const int page = table[j / page_size];                  // negative: a page behind every window, given back
     TC* out = dst + (size_t)(cu_kv[e] + j) * rank;
-    for (int i = threadIdx.x; i < rank; i += blockDim.x) out[i] = cache[row * width + i];
+    const size_t row = (size_t)(page < 0 ? 0 : page) * page_size + (j % page_size);
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) out[i] = page < 0 ? from_float<TC>(0.f) : cache[row * width + i];
   }
 }
 
@@ -294,14 +297,14 @@ extern "C" int srlm_latent_expand(const float* o_lat, const void* uv_t, int w_dt
 }
 
 extern "C" int srlm_latent_gather(const void* cache, int cache_dtype, void* dst, const int* block_table, int table_stride,
-                                  const int* cu_kv, int n_entries, int max_kv_len, int page_size, int width, int rank,
-                                  cudaStream_t stream) {
+                                  const int* cu_kv, const int* kv_first, const int* kv_lens, int n_entries, int max_kv_len,
+                                  int page_size, int width, int rank, cudaStream_t stream) {
   if (n_entries <= 0 || max_kv_len <= 0) return ST_OK;
   if (rank <= 0 || width < rank || page_size <= 0 || n_entries > 65535)
     return refuse(ST_BAD_SIZE, "latent_gather: rank=%d width=%d page_size=%d entries=%d", rank, width, page_size, n_entries);
   dim3 grid((unsigned)(max_kv_len < 4096 ? max_kv_len : 4096), (unsigned)n_entries);
   SRLM_DISPATCH_ACT(cache_dtype, TC, (launch_pdl(latent_gather_kernel<TC>, dim3(grid), dim3(64), 0, stream, 
-      (const TC*)cache, (TC*)dst, block_table, table_stride, cu_kv, page_size, width, rank)));
+      (const TC*)cache, (TC*)dst, block_table, table_stride, cu_kv, kv_first, kv_lens, page_size, width, rank)));
   return launched();
 }
 

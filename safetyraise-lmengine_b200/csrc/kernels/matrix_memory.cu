@@ -9,11 +9,15 @@
 // 1 / sqrt(d).  A request's state row: S [H][d][dv] | n [H][d] | m [H], zeros for a new request.
 //
 // matrix_memory_recurrence: a block takes one entry, one head and a tile of the value columns; the tiles of a head are a
-// thread-block cluster.  Eight lanes share a column of S (a lane holds the rows r = lane + 8 j in registers), so S^T q is
-// a sum in registers and three shuffles.  Every tile also carries n (it needs n . q); the first one writes it back.  All
-// tiles read n and m before any of them writes: the cluster's barrier behind the loads orders that.  Tokens come in
-// chunks through shared memory (cp.async, the next chunk in flight while this one is walked); the gates' transforms are
-// applied once per chunk.
+// thread-block cluster.  Its walking warps hold S: eight lanes share a column, a lane DPL neighbouring rows of it in
+// registers, so S^T q is a sum in registers and three shuffles.  One more warp, the helper, runs a chunk of tokens
+// ahead of them: it turns the chunk's gate logits into logarithms, walks m, forms exp(f + m - m') and exp(i - m') for
+// every token, carries n (a lane holds d / 32 rows) and forms n . q and with it 1 / denominator; the walkers read these
+// three numbers a token from shared memory and do nothing but S <- keep S + (write v) k and the read-out.  Every tile
+// carries n this way; the first one writes it back.  All tiles read n and m before any of them writes: the cluster's
+// barrier behind the loads orders that.  Tokens come in chunks of 16 through three buffers of shared memory (cp.async):
+// while the walkers are on chunk c the helper is on chunk c + 1 and chunk c + 2 is in flight; one barrier a chunk.
+// Rows of q and k lie in shared memory by lane, DPL + 4 floats apart, so that the lanes' 16-byte loads meet no bank twice.
 //
 // matrix_memory_output: per token and head o / sqrt(mean(o^2) + eps) * w * logistic(gate), a warp a head.
 #include "common.cuh"
@@ -39,110 +43,191 @@ __global__ void matrix_memory_recurrence_kernel(const float* __restrict__ proj, 
                                                 float* __restrict__ o_out, int H, int d, int dv, int cols) {
   pdl_wait();
   pdl_trigger();
-  extern __shared__ float mm_smem[];
-  // two buffers of: q [chunk][d] | k [chunk][d] | v [chunk][cols] | gates [chunk][2]
-  const int per_buf = kMemChunk * (2 * d + cols + 2);
+  extern __shared__ __align__(16) float mm_smem[];
+  constexpr int LS = DPL + 4;                      // a lane's rows, padded
+  constexpr int QS = kMemLanes * LS;               // a token's q (or k) row in shared memory
+  constexpr int DN = (kMemLanes * DPL + 31) / 32;  // rows of n a helper lane holds
+  // raw chunks, three buffers of: q [chunk][QS] | k [chunk][QS] | v [chunk][cols] | gate logits [chunk][2];
+  // then two buffers of what the helper makes of a chunk: keep | write | 1 / denominator [chunk] each; then its scratch
+  const int per_raw = kMemChunk * (2 * QS + cols + 2);
+  float* coef = mm_smem + 3 * per_raw;
+  float* part = coef + 2 * 3 * kMemChunk;          // [chunk][33]: the helper lanes' shares of n . q
   const int e = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * cols;
   const int first = cu_q[e], n_tok = cu_q[e + 1] - first;
+  const int walkers = cols * kMemLanes;            // threads that hold S; the last warp of the block is the helper
+  const bool helper = (int)threadIdx.x >= walkers;
+  const int lane = threadIdx.x & 31;
   const int col_local = threadIdx.x / kMemLanes, l = threadIdx.x % kMemLanes;
   const int col = c0 + col_local;
-  const bool live = col_local < cols && col < dv;
+  const bool live = !helper && col < dv;
   float* row = state + (size_t)slots[e] * state_stride;
   float* S_g = row + (size_t)h * d * dv;
   float* n_g = row + (size_t)H * d * dv + (size_t)h * d;
   float* m_g = row + (size_t)H * d * dv + (size_t)H * d + h;
   const int q_off = h * d, k_off = H * d + h * d, v_off = 2 * H * d + h * dv + c0, i_off = 2 * H * d + 2 * H * dv + h,
             f_off = i_off + H;
+  const int chunks = (n_tok + kMemChunk - 1) / kMemChunk;
+  const int rows_pad = kMemLanes * DPL;
 
-  auto fetch = [&](int chunk, int buf) {
-    float* base = mm_smem + buf * per_buf;
-    const int t0 = chunk * kMemChunk, cnt = min(kMemChunk, n_tok - t0);
-    for (int idx = threadIdx.x; idx < cnt * d; idx += blockDim.x) {
-      const int tt = idx / d, r = idx - tt * d;
-      const float* src = proj + (size_t)(first + t0 + tt) * ldp;
-      mm_cp_async_4(base + tt * d + r, src + q_off + r);
-      mm_cp_async_4(base + kMemChunk * d + tt * d + r, src + k_off + r);
-    }
-    for (int idx = threadIdx.x; idx < cnt * cols; idx += blockDim.x) {
-      const int tt = idx / cols, c = idx - tt * cols;
-      if (c0 + c < dv) mm_cp_async_4(base + 2 * kMemChunk * d + tt * cols + c, proj + (size_t)(first + t0 + tt) * ldp + v_off + c);
-    }
-    for (int idx = threadIdx.x; idx < cnt * 2; idx += blockDim.x) {
-      const int tt = idx >> 1, which = idx & 1;
-      mm_cp_async_4(base + kMemChunk * (2 * d + cols) + idx, proj + (size_t)(first + t0 + tt) * ldp + (which ? f_off : i_off));
+  auto fetch = [&](int chunk) {
+    if (chunk < chunks) {
+      float* base = mm_smem + (chunk % 3) * per_raw;
+      const int t0 = chunk * kMemChunk, cnt = min(kMemChunk, n_tok - t0);
+      for (int idx = threadIdx.x; idx < cnt * rows_pad; idx += blockDim.x) {
+        const int tt = idx / rows_pad, r = idx - tt * rows_pad;
+        const int at = tt * QS + (r / DPL) * LS + r % DPL;
+        if (r < d) {
+          const float* src = proj + (size_t)(first + t0 + tt) * ldp;
+          mm_cp_async_4(base + at, src + q_off + r);
+          mm_cp_async_4(base + kMemChunk * QS + at, src + k_off + r);
+        } else {
+          base[at] = 0.f;
+          base[kMemChunk * QS + at] = 0.f;
+        }
+      }
+      for (int idx = threadIdx.x; idx < cnt * cols; idx += blockDim.x) {
+        const int tt = idx / cols, c = idx - tt * cols;
+        if (c0 + c < dv) mm_cp_async_4(base + 2 * kMemChunk * QS + tt * cols + c, proj + (size_t)(first + t0 + tt) * ldp + v_off + c);
+      }
+      for (int idx = threadIdx.x; idx < cnt * 2; idx += blockDim.x)
+        mm_cp_async_4(base + kMemChunk * (2 * QS + cols) + idx,
+                      proj + (size_t)(first + t0 + (idx >> 1)) * ldp + ((idx & 1) ? f_off : i_off));
     }
     asm volatile("cp.async.commit_group;" ::);
   };
 
-  float S[DPL], nv[DPL];
+  // the helper's state: n (rows lane * DN + j) and m; the walkers': DPL rows of a column of S
+  float S[DPL], nv[DN];
+  float m = 0.f;
+  if (helper) {
 #pragma unroll
-  for (int j = 0; j < DPL; ++j) {
-    const int r = l + kMemLanes * j;
-    S[j] = (live && r < d) ? S_g[(size_t)r * dv + col] : 0.f;
-    nv[j] = r < d ? n_g[r] : 0.f;
+    for (int j = 0; j < DN; ++j) {
+      const int r = lane * DN + j;
+      nv[j] = r < d ? n_g[r] : 0.f;
+    }
+    m = *m_g;
+  } else {
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) {
+      const int r = l * DPL + j;
+      S[j] = (live && r < d) ? S_g[(size_t)r * dv + col] : 0.f;
+    }
   }
-  float m = *m_g;
-  const int chunks = (n_tok + kMemChunk - 1) / kMemChunk;
-  fetch(0, 0);
+  fetch(0);
+  fetch(1);
   mm_cluster_sync();                 // every tile of this head holds the old n and m before any tile writes new ones
   const float q_scale = rsqrtf((float)d);
-  for (int ch = 0; ch < chunks; ++ch) {
-    const int buf = ch & 1;
-    if (ch + 1 < chunks) {
-      fetch(ch + 1, buf ^ 1);
-      asm volatile("cp.async.wait_group 1;" ::);
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::);
-    }
-    __syncthreads();
-    float* base = mm_smem + buf * per_buf;
+
+  // what the helper makes of chunk ch (its raw data has landed and is visible): keep, write, 1 / denominator per token
+  auto prepare = [&](int ch) {
+    float* base = mm_smem + (ch % 3) * per_raw;
     const float* q_s = base;
-    const float* k_s = base + kMemChunk * d;
-    const float* v_s = base + 2 * kMemChunk * d;
-    float* g_s = base + kMemChunk * (2 * d + cols);
+    const float* k_s = base + kMemChunk * QS;
+    const float* g_s = base + kMemChunk * (2 * QS + cols);
+    float* cf = coef + (ch & 1) * 3 * kMemChunk;
     const int cnt = min(kMemChunk, n_tok - ch * kMemChunk);
-    if (threadIdx.x < 2 * cnt) {       // the gates' logarithms, once per token
-      const int which = threadIdx.x & 1;
-      const float z = cap * tanhf((g_s[threadIdx.x] + (which ? bias_f[h] : bias_i[h])) / cap);
-      // log logistic(z) = min(z, 0) - log1p(exp(-|z|))
-      g_s[threadIdx.x] = which ? fminf(z, 0.f) - log1pf(expf(-fabsf(z))) : z;
+    // the gates' logarithms, a lane a token
+    float gi = 0.f, gf = 0.f;
+    if (lane < cnt) {
+      gi = cap * tanhf((g_s[2 * lane] + bias_i[h]) / cap);
+      const float z = cap * tanhf((g_s[2 * lane + 1] + bias_f[h]) / cap);
+      gf = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));           // log logistic(z)
     }
-    __syncthreads();
+    // m walks the chunk; every lane follows it, lane t keeps token t's
+    float m_mine = 0.f, m_before = 0.f;
     for (int tt = 0; tt < cnt; ++tt) {
-      const float gi = g_s[2 * tt], gf = g_s[2 * tt + 1];
-      const float m_new = fmaxf(gf + m, gi);
-      const float keep = expf(gf + m - m_new), write = expf(gi - m_new);
+      const float fi = __shfl_sync(0xffffffffu, gi, tt), ff = __shfl_sync(0xffffffffu, gf, tt);
+      const float m_new = fmaxf(ff + m, fi);
+      if (lane == tt) { m_before = m; m_mine = m_new; }
       m = m_new;
-      const float wv = live ? write * v_s[tt * cols + col_local] : 0.f;
-      float acc_o = 0.f, acc_n = 0.f;
+    }
+    const float keep = expf(gf + m_before - m_mine), write = expf(gi - m_mine);
+    if (lane < cnt) {
+      cf[lane] = keep;
+      cf[kMemChunk + lane] = write;
+    }
+    // n walks the chunk; a lane's share of n . q of every token goes through shared memory to the token's lane
+    for (int tt = 0; tt < cnt; ++tt) {
+      const float kp = __shfl_sync(0xffffffffu, keep, tt), wr = __shfl_sync(0xffffffffu, write, tt);
+      float acc = 0.f;
 #pragma unroll
-      for (int j = 0; j < DPL; ++j) {
-        const int r = l + kMemLanes * j;
-        const float kk = r < d ? k_s[tt * d + r] : 0.f, qq = r < d ? q_s[tt * d + r] : 0.f;
-        S[j] = fmaf(keep, S[j], wv * kk);
-        nv[j] = fmaf(keep, nv[j], write * kk);
-        acc_o = fmaf(S[j], qq, acc_o);
-        acc_n = fmaf(nv[j], qq, acc_n);
+      for (int j = 0; j < DN; ++j) {
+        const int r = lane * DN + j;
+        const int at = tt * QS + (r / DPL) * LS + r % DPL;
+        const float kk = r < rows_pad ? k_s[at] : 0.f, qq = r < rows_pad ? q_s[at] : 0.f;
+        nv[j] = fmaf(kp, nv[j], wr * kk);
+        acc = fmaf(nv[j], qq, acc);
       }
+      part[tt * 33 + lane] = acc;
+    }
+    __syncwarp();
+    if (lane < cnt) {
+      float nq = 0.f;
+#pragma unroll 8
+      for (int i = 0; i < 32; ++i) nq += part[lane * 33 + i];
+      cf[2 * kMemChunk + lane] = q_scale / (fmaxf(fabsf(nq * q_scale), expf(-m_mine)) + floor_);
+    }
+    __syncwarp();
+  };
+
+  asm volatile("cp.async.wait_group 1;" ::);       // chunk 0 has landed
+  __syncthreads();
+  if (helper) prepare(0);
+  for (int ch = 0; ch < chunks; ++ch) {
+    asm volatile("cp.async.wait_group 0;" ::);     // chunk ch + 1 has landed (this thread's copies)
+    __syncthreads();                               // ... and everybody's; the helper's work on chunk ch is visible; nobody
+    fetch(ch + 2);                                 // reads chunk ch - 1 any more, whose buffer chunk ch + 2 takes
+    if (helper) {
+      if (ch + 1 < chunks) prepare(ch + 1);
+    } else {
+      const float* base = mm_smem + (ch % 3) * per_raw;
+      const float* q_s = base + l * LS;
+      const float* k_s = base + kMemChunk * QS + l * LS;
+      const float* v_s = base + 2 * kMemChunk * QS;
+      const float* cf = coef + (ch & 1) * 3 * kMemChunk;
+      const int cnt = min(kMemChunk, n_tok - ch * kMemChunk);
+      float* o_row = o_out + (size_t)(first + ch * kMemChunk) * H * dv + (size_t)h * dv + col;
+#pragma unroll 2
+      for (int tt = 0; tt < cnt; ++tt) {
+        const float keep = cf[tt];
+        const float wv = live ? cf[kMemChunk + tt] * v_s[tt * cols + col_local] : 0.f;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int o = 1; o < kMemLanes; o <<= 1) {
-        acc_o += __shfl_xor_sync(0xffffffffu, acc_o, o);
-        acc_n += __shfl_xor_sync(0xffffffffu, acc_n, o);
-      }
-      if (l == 0 && live) {
-        const float den = fmaxf(fabsf(acc_n * q_scale), expf(-m)) + floor_;
-        o_out[(size_t)(first + ch * kMemChunk + tt) * H * dv + (size_t)h * dv + col] = acc_o * q_scale / den;
+        for (int j = 0; j < DPL; j += 4) {
+          const float4 kk = *reinterpret_cast<const float4*>(k_s + tt * QS + j);
+          const float4 qq = *reinterpret_cast<const float4*>(q_s + tt * QS + j);
+          S[j] = fmaf(keep, S[j], wv * kk.x);
+          S[j + 1] = fmaf(keep, S[j + 1], wv * kk.y);
+          S[j + 2] = fmaf(keep, S[j + 2], wv * kk.z);
+          S[j + 3] = fmaf(keep, S[j + 3], wv * kk.w);
+          acc[0] = fmaf(S[j], qq.x, acc[0]);
+          acc[1] = fmaf(S[j + 1], qq.y, acc[1]);
+          acc[2] = fmaf(S[j + 2], qq.z, acc[2]);
+          acc[3] = fmaf(S[j + 3], qq.w, acc[3]);
+        }
+        float a = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+        for (int o = 1; o < kMemLanes; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (l == 0 && live) o_row[(size_t)tt * H * dv] = a * cf[2 * kMemChunk + tt];
       }
     }
-    __syncthreads();                   // the buffer is free for the chunk after the next
   }
+  if (helper) {
+    if (blockIdx.x == 0) {
 #pragma unroll
-  for (int j = 0; j < DPL; ++j) {
-    const int r = l + kMemLanes * j;
-    if (live && r < d) S_g[(size_t)r * dv + col] = S[j];
-    if (blockIdx.x == 0 && col_local == 0 && r < d) n_g[r] = nv[j];
+      for (int j = 0; j < DN; ++j) {
+        const int r = lane * DN + j;
+        if (r < d) n_g[r] = nv[j];
+      }
+      if (lane == 0) *m_g = m;
+    }
+  } else if (live) {
+#pragma unroll
+    for (int j = 0; j < DPL; ++j) {
+      const int r = l * DPL + j;
+      if (r < d) S_g[(size_t)r * dv + col] = S[j];
+    }
   }
-  if (blockIdx.x == 0 && threadIdx.x == 0) *m_g = m;
 }
 
 template <typename TO>
@@ -186,9 +271,12 @@ extern "C" int srlm_matrix_memory_recurrence(const float* proj, long long ldp, c
   if (tiles > 8) tiles = 8;
   int cols = ((dv + tiles - 1) / tiles + 3) / 4 * 4;
   tiles = (dv + cols - 1) / cols;
-  const int threads = cols * kMemLanes;
-  if (threads > 1024) return refuse(ST_BAD_SIZE, "matrix_memory_recurrence: vdim=%d (at most 1024)", dv);
-  const size_t smem = 2 * (size_t)kMemChunk * (2 * d + cols + 2) * sizeof(float);
+  const int threads = cols * kMemLanes + 32;      // the walkers and the helper warp
+  if (threads > 1024) return refuse(ST_BAD_SIZE, "matrix_memory_recurrence: vdim=%d (at most 992)", dv);
+  const int dpl_rows = (d + kMemLanes - 1) / kMemLanes;
+  const int dpl_t = dpl_rows <= 4 ? 4 : dpl_rows <= 8 ? 8 : dpl_rows <= 16 ? 16 : 32;
+  const size_t smem = ((size_t)3 * kMemChunk * (2 * kMemLanes * (dpl_t + 4) + cols + 2) + 2 * 3 * kMemChunk + kMemChunk * 33) *
+                      sizeof(float);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)tiles, (unsigned)H, (unsigned)n_entries);
   cfg.blockDim = dim3((unsigned)threads);
@@ -201,7 +289,7 @@ extern "C" int srlm_matrix_memory_recurrence(const float* proj, long long ldp, c
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const int dpl = (d + kMemLanes - 1) / kMemLanes;
+  const int dpl = dpl_t;
 #define SRLM_MM(DPL)                                                                                                     \
   do {                                                                                                                   \
     auto kern = matrix_memory_recurrence_kernel<DPL>;                                                                    \

@@ -1002,10 +1002,11 @@ class KernelLibrary:
                                                   C.c_int(pairs_per_token), _ptr(out), C.c_int(out.shape[0]),
                                                   C.c_int(out.shape[1]), _ptr(pair_scale), _stream()), "moe_gather_rows")
 
-    def gemm_tn_tcgen05_grouped(self, x, w, out, group_of_tile, glu=False, limit=0.0, alpha=0.0, tile_rows=128):
+    def gemm_tn_tcgen05_grouped(self, x, w, out, group_of_tile, glu=False, limit=0.0, alpha=0.0, tile_rows=128, act=None):
         """out[r] = x[r] . w[group of r's tile]^T on the persistent tensor-memory kernel: x [rows, K] bfloat16 in tiles
         of tile_rows rows (128, or 256: pairs of SMs), w [groups, N, K]; a tile whose group is negative is skipped.
-        glu: w's rows in blocks of 8 gate and 8 up rows, out [rows, N / 2] = the clamped GLU."""
+        glu: w's rows in blocks of 8 gate and 8 up rows, out [rows, N / 2] = the clamped GLU.  act "gelu" (without glu):
+        out = the exact gelu of the product."""
         rows, K = x.shape
         G, N, _ = w.shape
         if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[2] != K or group_of_tile.numel() * tile_rows < rows:
@@ -1015,7 +1016,8 @@ class KernelLibrary:
             _ptr(x), _ptr(w), _ptr(out), dtype_code(out.dtype), C.c_int(rows), C.c_int(N), C.c_int(K),
             C.c_longlong(x.stride(0)), C.c_longlong(out.stride(0)), C.c_int(G), _ptr(group_of_tile), C.c_int(tile_rows),
             C.c_int(int(glu)),
-            C.c_float(limit), C.c_float(alpha), _ptr(err), _stream()), "gemm_tn_tcgen05_grouped")
+            C.c_float(limit), C.c_float(alpha), C.c_int(self.PLAIN_ACTIVATIONS[act]), _ptr(err), _stream()),
+            "gemm_tn_tcgen05_grouped")
 
     PLAIN_ACTIVATIONS = {None: 0, "gelu": 1}
 
@@ -1200,15 +1202,16 @@ class KernelLibrary:
                                                    _ptr(rate), _ptr(a_out), _ptr(b_out), C.c_int(T), C.c_int(Cn),
                                                    C.c_int(blocks), _stream()), "recurrence_gates")
 
-    def linear_recurrence(self, ctx, a, b, y, y_column, y_bias, state, out):
+    def linear_recurrence(self, ctx, a, b, y, y_column, y_bias, state, out, in_segments=False):
         """S <- a S + b per channel and token, from the slots' S (the first C floats of a row of ``state``), renewed at
-        the end; out [T, C] = S * gelu_tanh(y[:, y_column : + C] + y_bias)."""
+        the end; out [T, C] = S * gelu_tanh(y[:, y_column : + C] + y_bias).  in_segments: every entry's tokens in 32
+        segments walked side by side (for long portions; the sums are formed in another order)."""
         T, Cn = a.shape
         ptr, ld = self._columns(y, y_column, Cn)
         self._check(self.lib.srlm_linear_recurrence(_ptr(a), _ptr(b), ptr, ld, _ptr(y_bias), _ptr(state),
                                                     C.c_longlong(state.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.slots),
                                                     _ptr(out), dtype_code(out.dtype), C.c_int(ctx.n_entries), C.c_int(Cn),
-                                                    _stream()), "linear_recurrence")
+                                                    C.c_int(int(in_segments)), _stream()), "linear_recurrence")
 
     # ---- attention over a cached latent ----------------------------------------------------
     def latent_append(self, proj, c_off, norm_w, eps, rotation, cache, kv_slot, rank, rot):
@@ -1244,12 +1247,13 @@ class KernelLibrary:
         return bool(self.latent_prompts_in_head_space and self.general_attention_on_tensor_cores
                     and self.lib.srlm_latent_prefill_attention_takes(C.c_int(dim), C.c_int(rot), C.c_int(dv), C.c_int(rank)))
 
-    def latent_gather(self, ctx, cache, dst, block_table, cu_kv, rank):
-        """dst[cu_kv[e] + j] = the latent (first ``rank`` elements of the page row) of key j of entry e."""
+    def latent_gather(self, ctx, cache, dst, block_table, cu_kv, rank, kv_first=None):
+        """dst[cu_kv[e] + j] = the latent (first ``rank`` elements of the page row) of key j of entry e, for j from
+        kv_first[e] (None: 0) on; zeros where the page has been given back."""
         self._check(self.lib.srlm_latent_gather(
             _ptr(cache), dtype_code(cache.dtype), _ptr(dst), _ptr(block_table), C.c_int(block_table.stride(0)),
-            _ptr(cu_kv), C.c_int(ctx.n_entries), C.c_int(ctx.max_kv_len), C.c_int(cache.shape[2]),
-            C.c_int(cache.shape[3]), C.c_int(rank), _stream()), "latent_gather")
+            _ptr(cu_kv), _ptr(kv_first), _ptr(ctx.kv_lens), C.c_int(ctx.n_entries), C.c_int(ctx.max_kv_len),
+            C.c_int(cache.shape[2]), C.c_int(cache.shape[3]), C.c_int(rank), _stream()), "latent_gather")
 
     def latent_rotate_q(self, proj, rotation, q_out, heads, dim, rot):
         pairs = rotation.pairs if rotation is not None else 0
@@ -1259,7 +1263,7 @@ class KernelLibrary:
             _ptr(q_out), C.c_int(proj.shape[0]), C.c_int(heads), C.c_int(dim), C.c_int(rot), _stream()), "latent_rotate_q")
 
     def latent_prefill_attention(self, ctx, q, pages, kv_rows, cu_kv, out, block_table, heads, dim, rot, dv, rank,
-                                 v_off, scale):
+                                 v_off, scale, window=0):
         """Causal attention of prompts in the heads' own space: q float32 [T, heads * (dim + rot)]; kv_rows bfloat16
         [keys of all entries, >= v_off + heads * dv] with the heads' unrotated keys and, from column v_off, values;
         the rotated key part comes from the pages."""
@@ -1267,7 +1271,7 @@ class KernelLibrary:
             _ptr(q), _ptr(pages), _ptr(kv_rows), C.c_longlong(kv_rows.stride(0)), _ptr(cu_kv), _ptr(out),
             dtype_code(out.dtype), _ptr(block_table), C.c_int(block_table.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.kv_lens),
             C.c_int(ctx.n_entries), C.c_int(ctx.max_q_len), C.c_int(heads), C.c_int(dim), C.c_int(rot), C.c_int(dv),
-            C.c_int(rank), C.c_int(v_off), C.c_int(pages.shape[2]), C.c_float(scale), _stream()),
+            C.c_int(rank), C.c_int(v_off), C.c_int(pages.shape[2]), C.c_float(scale), C.c_int(window or 0), _stream()),
             "latent_prefill_attention")
 
     def head_gate(self, x, proj, g_off, out, heads, dv):

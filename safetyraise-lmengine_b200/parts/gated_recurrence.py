@@ -73,5 +73,7 @@ class GatedLinearRecurrence(Part):
         b = ws.get("recurrence.b", T, C, torch.float32)
         ops.recurrence_gates(u, self.Ra, self.Ri, self.ba, self.bi, self.rate, a, b, s.blocks)
         gated = ws.get("recurrence.out", T, C, ctx.dtype)
-        ops.linear_recurrence(ctx, a, b, proj, 0, self.y_bias, state, gated)
+        # long portions in segments side by side; the float32 path walks token by token (its sums keep one order)
+        ops.linear_recurrence(ctx, a, b, proj, 0, self.y_bias, state, gated,
+                              in_segments=ctx.dtype != torch.float32 and ctx.max_q_len >= 256)
         return self.out(ctx, gated, "recurrence.proj_out", out_dtype=out_dtype)

@@ -115,9 +115,9 @@ class LatentAttention(Part):
             ops.rmsnorm_columns(proj, 0, s.q_rank, self.q_norm_w, s.latent_norm_eps, cq)
             q_heads = self.q_up(ctx, cq, "latent.q_heads_raw", out_dtype=torch.float32)
         gated = ctx.workspace.get("latent.out", T, s.heads * s.v_head_dim, ctx.dtype)
-        if (self.up_kv is not None and ctx.max_q_len > 4 and s.own_kv and not s.window and s.output_gate and not s.q_rank
+        if (self.up_kv is not None and ctx.max_q_len > 4
                 and ops.latent_prompt_takes(s.head_dim, s.rot_dim, s.v_head_dim, s.kv_rank)):
-            self._attend_in_head_space(ctx, proj, cache, group, rot, gated)
+            self._attend_in_head_space(ctx, proj, q_heads, cache, group, rot, gated)
             return self.out(ctx, gated, "latent.proj_out")
         qd = s.kv_rank + s.rot_dim
         q = ctx.workspace.get("latent.q", T, s.heads * qd, torch.float32)
@@ -128,27 +128,33 @@ class LatentAttention(Part):
         ops.latent_expand(o_lat, self.uv_t, proj, self.g_off, gated, s.heads, s.kv_rank, s.v_head_dim)
         return self.out(ctx, gated, "latent.proj_out")
 
-    def _attend_in_head_space(self, ctx, proj, cache, group, rot, gated) -> None:
-        """Prompts: gather the contexts' latents, form all heads' unrotated keys and values with one product,
-        attend per head, gate.  The row of key j of entry e in the gathered matrices is cu_kv[e] + j."""
+    def _attend_in_head_space(self, ctx, proj, q_heads, cache, group, rot, gated) -> None:
+        """Prompts: gather the contexts' latents (from the first key that the step's rows still see), form all heads'
+        unrotated keys and values with one product, attend per head, gate.  Key j of entry e lies in row cu_kv[e] + j
+        of the gathered matrices."""
         s = self.spec
         T = proj.shape[0]
-        cu_kv = ctx.tables.get("latent.cu_kv")
-        if cu_kv is None:
-            sums = [0]
-            for n in ctx.host["kv_lens"]:
-                sums.append(sums[-1] + n)
-            cu_kv = ctx.tables["latent.cu_kv"] = torch.tensor(sums, dtype=torch.int32).pin_memory().to(
-                proj.device, non_blocking=True)
-            ctx.tables["latent.keys"] = sums[-1]
-        keys = ctx.tables["latent.keys"]
+        key = ("latent.cu_kv", s.window)
+        if key not in ctx.tables:
+            cu, first, total = [], [], 0
+            for n, q_len in zip(ctx.host["kv_lens"], ctx.host["q_lens"]):
+                f = max(0, n - q_len - s.window + 1) if s.window else 0
+                cu.append(total - f)
+                first.append(f)
+                total += n - f
+            both = torch.tensor([cu, first], dtype=torch.int32).pin_memory().to(proj.device, non_blocking=True)
+            ctx.tables[key] = (both[0], both[1], total)
+        cu_kv, kv_first, keys = ctx.tables[key]
         latents = ctx.workspace.get("latent.gathered", keys, s.kv_rank, ctx.dtype)
-        ops.latent_gather(ctx, cache, latents, ctx.block_tables[group], cu_kv, s.kv_rank)
+        ops.latent_gather(ctx, cache, latents, ctx.block_tables[group], cu_kv, s.kv_rank, kv_first)
         kv_rows = ctx.workspace.get("latent.kv_rows", keys, s.heads * (s.head_dim + s.v_head_dim), ctx.dtype)
         ops.gemm(latents, self.up_kv, kv_rows)
         q = ctx.workspace.get("latent.q_heads", T, s.heads * (s.head_dim + s.rot_dim), torch.float32)
-        ops.latent_rotate_q(proj, rot, q, s.heads, s.head_dim, s.rot_dim)
-        attended = ctx.workspace.get("latent.o_heads", T, s.heads * s.v_head_dim, torch.float32)
+        ops.latent_rotate_q(q_heads, rot, q, s.heads, s.head_dim, s.rot_dim)
+        # without a gate the attention writes the output projection's input itself
+        attended = ctx.workspace.get("latent.o_heads", T, s.heads * s.v_head_dim, torch.float32) if s.output_gate else gated
         ops.latent_prefill_attention(ctx, q, cache, kv_rows, cu_kv, attended, ctx.block_tables[group], s.heads,
-                                     s.head_dim, s.rot_dim, s.v_head_dim, s.kv_rank, s.heads * s.head_dim, s.softmax_scale)
-        ops.head_gate(attended, proj, self.g_off, gated, s.heads, s.v_head_dim)
+                                     s.head_dim, s.rot_dim, s.v_head_dim, s.kv_rank, s.heads * s.head_dim, s.softmax_scale,
+                                     s.window or 0)
+        if s.output_gate:
+            ops.head_gate(attended, proj, self.g_off, gated, s.heads, s.v_head_dim)

@@ -64,6 +64,7 @@ class RoutedExperts(Part):
             pair = lambda g, u: torch.stack([g.view(I // 8, 8, H), u.view(I // 8, 8, H)], dim=1).reshape(2 * I, H)
         else:
             pair = lambda g, u: torch.cat([g, u], dim=0)
+        self.in_tiles = self.interleaved         # steps of many tokens may run the experts' products in whole tiles
         self.gate_up = torch.stack([pair(g, u) for g, u in zip(each(nm.gate), each(nm.up))]).contiguous()
         self.down = torch.stack(each(nm.down)).contiguous()
         # one product for everything that reads the layer's input whole: the shared expert's gate rows, its up
@@ -84,6 +85,9 @@ class RoutedExperts(Part):
         self.router_bias = tensors[p + nm.router_bias] if spec.router_bias else None
         self.interleaved = False
         self.limit = 0.0
+        I, H = spec.intermediate_size, spec.hidden_size
+        self.in_tiles = (mctx.dtype == torch.bfloat16 and I % 8 == 0 and H % 8 == 0
+                         and tensors[p + nm.expert.format(0) + nm.up].dtype == torch.bfloat16)
         self.gate_up = torch.stack(each(nm.up)).contiguous()
         self.down = torch.stack(each(nm.down)).contiguous()
         first, self.shared_down = [tensors[p + nm.router]], None
@@ -130,7 +134,7 @@ class RoutedExperts(Part):
         weight = ws.get("moe.weight", T, s.top, torch.float32)
         # steps of many tokens (64 rows an expert on average): the experts' products on the persistent tensor-memory
         # kernel, every expert's rows in whole tiles of 128 of a gathered copy of the input
-        if (self.interleaved and ops.grouped_products_in_tensor_memory and pairs >= 64 * s.experts
+        if (self.in_tiles and ops.grouped_products_in_tensor_memory and pairs >= 64 * s.experts
                 and s.intermediate_size % 8 == 0):
             ops.moe_route(first, self.router_bias, s.top, choice, weight, column=self.router_column, experts=s.experts,
                           scoring=s.scoring, groups=self.groups)
@@ -176,7 +180,7 @@ class RoutedExperts(Part):
         s = self.spec
         T, H = x.shape
         ws = ctx.workspace
-        tile = ops.grouped_tile_rows(T * s.top, s.experts, 2 * s.intermediate_size * H)
+        tile = ops.grouped_tile_rows(T * s.top, s.experts, (2 if s.gated else 1) * s.intermediate_size * H)
         n_tiles = (T * s.top) // tile + s.experts            # every expert wastes less than one tile
         rows_cap = n_tiles * tile
         heads = ws.get("moe.heads", 2, s.experts + 1, torch.int32, reserve=2)
@@ -188,8 +192,11 @@ class RoutedExperts(Part):
         xs = ws.get("moe.xs", rows_cap, H, ctx.dtype, reserve=0)
         ops.moe_gather_rows(x, pair_of_row, s.top, xs, pair_scale=weight if s.weight_on_input else None)
         y = ws.get("moe.y_tiles", rows_cap, s.intermediate_size, ctx.dtype, reserve=0)
-        ops.gemm_tn_tcgen05_grouped(xs, self.gate_up, y, group_of_tile, glu=True, limit=self.limit, alpha=s.glu_alpha,
-                                    tile_rows=tile)
+        if s.gated:
+            ops.gemm_tn_tcgen05_grouped(xs, self.gate_up, y, group_of_tile, glu=True, limit=self.limit, alpha=s.glu_alpha,
+                                        tile_rows=tile)
+        else:
+            ops.gemm_tn_tcgen05_grouped(xs, self.gate_up, y, group_of_tile, act=s.activation, tile_rows=tile)
         rows = ws.get("moe.rows_tiles", rows_cap, H, torch.float32, reserve=0)
         ops.gemm_tn_tcgen05_grouped(y, self.down, rows, group_of_tile, tile_rows=tile)
         out = ws.get("moe.out", T, H, ctx.dtype)

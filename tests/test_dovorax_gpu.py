@@ -667,10 +667,12 @@ def test_memory_read_out_normed_and_gated(dtype):
     assert (out.float().cpu() - ref).abs().max() <= (1e-5 if dtype == torch.float32 else 1e-2) * ref.abs().max()
 
 
+@pytest.mark.parametrize("segments", [False, True])
 @pytest.mark.parametrize("C,blocks,w_dtype", [(48, 3, torch.float32), (27, 1, torch.bfloat16), (10, 10, torch.float32),
                                               (256, 2, torch.bfloat16), (130, 1, torch.float32)])
-def test_gated_recurrence_carried_through_steps_and_slots(C, blocks, w_dtype):
-    """Decays from nearly one to nearly zero; a sequence in portions beside another request, against the plain loop."""
+def test_gated_recurrence_carried_through_steps_and_slots(C, blocks, w_dtype, segments):
+    """Decays from nearly one to nearly zero; a sequence in portions beside another request, against the plain loop;
+    token by token, and with every portion cut into segments that are walked side by side."""
     from safetyraise_lmengine_b200.kernels import ops
     dev, Cb = "cuda:0", C // blocks
     g = torch.Generator().manual_seed(C)
@@ -705,7 +707,7 @@ def test_gated_recurrence_carried_through_steps_and_slots(C, blocks, w_dtype):
         a, b = torch.empty_like(uu), torch.empty_like(uu)
         ops.recurrence_gates(uu, Ra.to(dev), Ri.to(dev), ba.to(dev), bi.to(dev), rate.to(dev), a, b, blocks)
         out = torch.empty_like(uu)
-        ops.linear_recurrence(ctx, a, b, yy, 3, yb.to(dev), state, out)
+        ops.linear_recurrence(ctx, a, b, yy, 3, yb.to(dev), state, out, in_segments=segments)
         at = 0
         for s, n in zip(live, sizes):
             got[s].append(out[at:at + n].cpu())
@@ -865,6 +867,41 @@ def test_experts_without_a_gate(dtype):
     out = torch.empty(T, H, device=dev, dtype=dtype)
     ops.moe_combine(rows, rop.view(T, top), weight.to(dev), shared.to(dev), out)
     assert (out.float().cpu() - ref).abs().max() <= (2e-5 if dtype == torch.float32 else 2e-2) * ref.abs().max()
+
+
+@pytest.mark.parametrize("tile", [128, 256])
+def test_experts_without_a_gate_in_tiles_of_tensor_memory(tile):
+    """Steps of many tokens: every expert's rows in whole tiles, both products on the persistent tensor-memory kernel
+    with the exact gelu in the first one's epilogue."""
+    from safetyraise_lmengine_b200.kernels import ops
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(15)
+    for T, E, top, H, ff in ((700, 5, 2, 64, 48), (130, 3, 1, 136, 200), (512, 4, 4, 256, 128)):
+        x = torch.randn(T, H, generator=g).bfloat16()
+        up = (0.4 * torch.randn(E, ff, H, generator=g)).bfloat16()
+        dn = (0.3 * torch.randn(E, H, ff, generator=g)).bfloat16()
+        choice = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32)
+        weight, shared = torch.rand(T, top, generator=g), torch.randn(T, H, generator=g).bfloat16()
+        n = T * top
+        n_tiles = n // tile + E
+        d = lambda t: t.to(dev)
+        heads = torch.zeros(2, E + 1, dtype=torch.int32, device=dev)
+        group = torch.full((n_tiles,), -7, dtype=torch.int32, device=dev)
+        por = torch.full((n_tiles * tile,), -7, dtype=torch.int32, device=dev)
+        rop = torch.zeros(n, dtype=torch.int32, device=dev)
+        ops.moe_sort(d(choice), E, heads[0], heads[1], por, rop, tile_rows=tile, group_of_tile=group)
+        xs = torch.empty(n_tiles * tile, H, dtype=torch.bfloat16, device=dev)
+        ops.moe_gather_rows(d(x), por, top, xs)
+        y = torch.zeros(n_tiles * tile, ff, dtype=torch.bfloat16, device=dev)
+        ops.gemm_tn_tcgen05_grouped(xs, d(up), y, group, act="gelu", tile_rows=tile)
+        rows = torch.zeros(n_tiles * tile, H, device=dev)
+        ops.gemm_tn_tcgen05_grouped(y, d(dn), rows, group, tile_rows=tile)
+        out = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
+        ops.moe_combine(rows, rop.view(T, top), d(weight), d(shared), out)
+        assert ops.gemm_error_flag(torch.device(dev)) == 0
+        want = _experts_plain(x.float(), up.float(), dn.float(), choice, weight.double(), shared.float())
+        err = (out.cpu().double() - want).abs().max() / want.abs().max()
+        assert err < 2e-2, (T, E, top, float(err))
 
 
 def test_command_line_and_trace_replay(tmp_path, tmp_path_factory):

@@ -75,8 +75,16 @@ recurrence_gates_kernel(const float* __restrict__ u, const TW* __restrict__ Ra, 
 #pragma unroll
     for (int kk = 0; kk < GK; ++kk) {
       float uv[PT];
+      if constexpr (PT % 4 == 0) {
 #pragma unroll
-      for (int i = 0; i < PT; ++i) uv[i] = Us[kk][ty * PT + i];
+        for (int i = 0; i < PT; i += 4) {
+          const float4 u4 = *reinterpret_cast<const float4*>(&Us[kk][ty * PT + i]);
+          uv[i] = u4.x; uv[i + 1] = u4.y; uv[i + 2] = u4.z; uv[i + 3] = u4.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < PT; ++i) uv[i] = Us[kk][ty * PT + i];
+      }
       const float4 wa = *reinterpret_cast<const float4*>(&Wa[kk][tx * 4]);
       const float4 wi = *reinterpret_cast<const float4*>(&Wi[kk][tx * 4]);
 #pragma unroll
@@ -231,7 +239,8 @@ extern "C" int srlm_recurrence_gates(const float* u, const void* Ra, const void*
   if (C <= 0 || blocks <= 0 || C % blocks || blocks > 65535)
     return refuse(ST_BAD_SIZE, "recurrence_gates: %d channels in %d blocks", C, blocks);
   const int Cb = C / blocks;
-  const int tt = T > 16 ? 64 : 16;           // token tile: steps of a few tokens run one token a thread
+  const int tt = T > 16 ? 64 : 16;           // token tile: steps of a few tokens run one token a thread (tiles of 128
+                                             // tokens, eight a thread, measured slower: 183 registers, one block an SM)
   dim3 grid((unsigned)((Cb + GN - 1) / GN), (unsigned)blocks, (unsigned)((T + tt - 1) / tt));
   if (grid.z > 65535) return refuse(ST_BAD_SIZE, "recurrence_gates: %d tokens", T);
   if (tt == 64)

@@ -9,15 +9,15 @@
 // 1 / sqrt(d).  A request's state row: S [H][d][dv] | n [H][d] | m [H], zeros for a new request.
 //
 // matrix_memory_recurrence: a block takes one entry, one head and a tile of the value columns; the tiles of a head are a
-// thread-block cluster.  Its walking warps hold S: eight lanes share a column, a lane DPL neighbouring rows of it in
-// registers, so S^T q is a sum in registers and three shuffles.  One more warp, the helper, runs a chunk of tokens
+// thread-block cluster.  Its walking warps hold S: sixteen lanes share a column, a lane DPL neighbouring rows of it in
+// registers, so S^T q is a sum in registers and four shuffles.  One more warp, the helper, runs a chunk of tokens
 // ahead of them: it turns the chunk's gate logits into logarithms, walks m, forms exp(f + m - m') and exp(i - m') for
 // every token, carries n (a lane holds d / 32 rows) and forms n . q and with it 1 / denominator; the walkers read these
 // three numbers a token from shared memory and do nothing but S <- keep S + (write v) k and the read-out.  Every tile
 // carries n this way; the first one writes it back.  All tiles read n and m before any of them writes: the cluster's
 // barrier behind the loads orders that.  Tokens come in chunks of 16 through three buffers of shared memory (cp.async):
 // while the walkers are on chunk c the helper is on chunk c + 1 and chunk c + 2 is in flight; one barrier a chunk.
-// Rows of q and k lie in shared memory by lane, DPL + 4 floats apart, so that the lanes' 16-byte loads meet no bank twice.
+// Rows of q and k lie in shared memory by lane, a few floats apart, so that the lanes' 16-byte loads meet no bank twice.
 //
 // matrix_memory_output: per token and head o / sqrt(mean(o^2) + eps) * w * logistic(gate), a warp a head.
 #include "common.cuh"
@@ -25,11 +25,15 @@
 namespace srlm {
 
 constexpr int kMemChunk = 16;       // tokens of a chunk
-constexpr int kMemLanes = 8;        // lanes of a column
+constexpr int kMemLanes = 16;       // lanes of a column
 
 __device__ __forceinline__ void mm_cp_async_4(float* dst, const float* src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src));
+}
+__device__ __forceinline__ void mm_cp_async_16(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src));
 }
 __device__ __forceinline__ void mm_cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -40,11 +44,11 @@ __global__ void matrix_memory_recurrence_kernel(const float* __restrict__ proj, 
                                                 const float* __restrict__ bias_f, float cap, float floor_,
                                                 float* __restrict__ state, long long state_stride,
                                                 const int* __restrict__ cu_q, const int* __restrict__ slots,
-                                                float* __restrict__ o_out, int H, int d, int dv, int cols) {
+                                                float* __restrict__ o_out, int H, int d, int dv, int cols, int vec) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ __align__(16) float mm_smem[];
-  constexpr int LS = DPL + 4;                      // a lane's rows, padded
+  constexpr int LS = DPL == 4 ? 4 : DPL + 4;       // a lane's rows, padded (8 lanes' 16-byte loads then meet 8 groups of banks)
   constexpr int QS = kMemLanes * LS;               // a token's q (or k) row in shared memory
   constexpr int DN = (kMemLanes * DPL + 31) / 32;  // rows of n a helper lane holds
   // raw chunks, three buffers of: q [chunk][QS] | k [chunk][QS] | v [chunk][cols] | gate logits [chunk][2];
@@ -73,21 +77,42 @@ __global__ void matrix_memory_recurrence_kernel(const float* __restrict__ proj, 
     if (chunk < chunks) {
       float* base = mm_smem + (chunk % 3) * per_raw;
       const int t0 = chunk * kMemChunk, cnt = min(kMemChunk, n_tok - t0);
-      for (int idx = threadIdx.x; idx < cnt * rows_pad; idx += blockDim.x) {
-        const int tt = idx / rows_pad, r = idx - tt * rows_pad;
-        const int at = tt * QS + (r / DPL) * LS + r % DPL;
-        if (r < d) {
-          const float* src = proj + (size_t)(first + t0 + tt) * ldp;
-          mm_cp_async_4(base + at, src + q_off + r);
-          mm_cp_async_4(base + kMemChunk * QS + at, src + k_off + r);
-        } else {
-          base[at] = 0.f;
-          base[kMemChunk * QS + at] = 0.f;
+      if (vec) {        // 16-byte copies: four neighbouring rows of q and of k, four neighbouring columns of v
+        constexpr int RP4 = kMemLanes * DPL / 4;
+        for (int idx = threadIdx.x; idx < cnt * RP4; idx += blockDim.x) {
+          const int tt = idx / RP4, r = (idx - tt * RP4) * 4;
+          const int at = tt * QS + (r / DPL) * LS + r % DPL;
+          if (r < d) {
+            const float* src = proj + (size_t)(first + t0 + tt) * ldp;
+            mm_cp_async_16(base + at, src + q_off + r);
+            mm_cp_async_16(base + kMemChunk * QS + at, src + k_off + r);
+          } else {
+            *reinterpret_cast<float4*>(base + at) = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4*>(base + kMemChunk * QS + at) = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
         }
-      }
-      for (int idx = threadIdx.x; idx < cnt * cols; idx += blockDim.x) {
-        const int tt = idx / cols, c = idx - tt * cols;
-        if (c0 + c < dv) mm_cp_async_4(base + 2 * kMemChunk * QS + tt * cols + c, proj + (size_t)(first + t0 + tt) * ldp + v_off + c);
+        const int c4 = cols / 4;
+        for (int idx = threadIdx.x; idx < cnt * c4; idx += blockDim.x) {
+          const int tt = idx / c4, c = (idx - tt * c4) * 4;
+          if (c0 + c < dv) mm_cp_async_16(base + 2 * kMemChunk * QS + tt * cols + c, proj + (size_t)(first + t0 + tt) * ldp + v_off + c);
+        }
+      } else {
+        for (int idx = threadIdx.x; idx < cnt * rows_pad; idx += blockDim.x) {
+          const int tt = idx / rows_pad, r = idx - tt * rows_pad;
+          const int at = tt * QS + (r / DPL) * LS + r % DPL;
+          if (r < d) {
+            const float* src = proj + (size_t)(first + t0 + tt) * ldp;
+            mm_cp_async_4(base + at, src + q_off + r);
+            mm_cp_async_4(base + kMemChunk * QS + at, src + k_off + r);
+          } else {
+            base[at] = 0.f;
+            base[kMemChunk * QS + at] = 0.f;
+          }
+        }
+        for (int idx = threadIdx.x; idx < cnt * cols; idx += blockDim.x) {
+          const int tt = idx / cols, c = idx - tt * cols;
+          if (c0 + c < dv) mm_cp_async_4(base + 2 * kMemChunk * QS + tt * cols + c, proj + (size_t)(first + t0 + tt) * ldp + v_off + c);
+        }
       }
       for (int idx = threadIdx.x; idx < cnt * 2; idx += blockDim.x)
         mm_cp_async_4(base + kMemChunk * (2 * QS + cols) + idx,
@@ -123,49 +148,63 @@ __global__ void matrix_memory_recurrence_kernel(const float* __restrict__ proj, 
     float* base = mm_smem + (ch % 3) * per_raw;
     const float* q_s = base;
     const float* k_s = base + kMemChunk * QS;
-    const float* g_s = base + kMemChunk * (2 * QS + cols);
+    float* g_s = base + kMemChunk * (2 * QS + cols);
     float* cf = coef + (ch & 1) * 3 * kMemChunk;
     const int cnt = min(kMemChunk, n_tok - ch * kMemChunk);
-    // the gates' logarithms, a lane a token
+    // the gates' logarithms, a lane a token, in place
     float gi = 0.f, gf = 0.f;
     if (lane < cnt) {
       gi = cap * tanhf((g_s[2 * lane] + bias_i[h]) / cap);
       const float z = cap * tanhf((g_s[2 * lane + 1] + bias_f[h]) / cap);
       gf = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));           // log logistic(z)
+      g_s[2 * lane] = gi;
+      g_s[2 * lane + 1] = gf;
     }
-    // m walks the chunk; every lane follows it, lane t keeps token t's
+    __syncwarp();
+    // m walks the chunk in every lane's registers; lane t keeps token t's
     float m_mine = 0.f, m_before = 0.f;
-    for (int tt = 0; tt < cnt; ++tt) {
-      const float fi = __shfl_sync(0xffffffffu, gi, tt), ff = __shfl_sync(0xffffffffu, gf, tt);
-      const float m_new = fmaxf(ff + m, fi);
-      if (lane == tt) { m_before = m; m_mine = m_new; }
-      m = m_new;
-    }
-    const float keep = expf(gf + m_before - m_mine), write = expf(gi - m_mine);
-    if (lane < cnt) {
-      cf[lane] = keep;
-      cf[kMemChunk + lane] = write;
-    }
-    // n walks the chunk; a lane's share of n . q of every token goes through shared memory to the token's lane
-    for (int tt = 0; tt < cnt; ++tt) {
-      const float kp = __shfl_sync(0xffffffffu, keep, tt), wr = __shfl_sync(0xffffffffu, write, tt);
-      float acc = 0.f;
 #pragma unroll
-      for (int j = 0; j < DN; ++j) {
-        const int r = lane * DN + j;
-        const int at = tt * QS + (r / DPL) * LS + r % DPL;
-        const float kk = r < rows_pad ? k_s[at] : 0.f, qq = r < rows_pad ? q_s[at] : 0.f;
-        nv[j] = fmaf(kp, nv[j], wr * kk);
-        acc = fmaf(nv[j], qq, acc);
+    for (int tt = 0; tt < kMemChunk; ++tt) {
+      if (tt < cnt) {
+        const float m_new = fmaxf(g_s[2 * tt + 1] + m, g_s[2 * tt]);
+        if (lane == tt) { m_before = m; m_mine = m_new; }
+        m = m_new;
       }
-      part[tt * 33 + lane] = acc;
+    }
+    if (lane < cnt) {
+      cf[lane] = expf(gf + m_before - m_mine);
+      cf[kMemChunk + lane] = expf(gi - m_mine);
+    }
+    __syncwarp();
+    // n walks the chunk; a lane's share of n . q of every token goes through shared memory to the token's lane.  A lane's
+    // DN rows are neighbours within one walker lane's rows.
+    const int off = ((lane * DN) / DPL) * LS + (lane * DN) % DPL;
+#pragma unroll
+    for (int tt = 0; tt < kMemChunk; ++tt) {
+      if (tt < cnt) {
+        const float kp = cf[tt], wr = cf[kMemChunk + tt];
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < DN; ++j) {
+          const float kk = k_s[tt * QS + off + j], qq = q_s[tt * QS + off + j];
+          nv[j] = fmaf(kp, nv[j], wr * kk);
+          acc = fmaf(nv[j], qq, acc);
+        }
+        part[tt * 33 + lane] = acc;
+      }
     }
     __syncwarp();
     if (lane < cnt) {
-      float nq = 0.f;
-#pragma unroll 8
-      for (int i = 0; i < 32; ++i) nq += part[lane * 33 + i];
-      cf[2 * kMemChunk + lane] = q_scale / (fmaxf(fabsf(nq * q_scale), expf(-m_mine)) + floor_);
+      float nq[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        nq[0] += part[lane * 33 + i];
+        nq[1] += part[lane * 33 + i + 1];
+        nq[2] += part[lane * 33 + i + 2];
+        nq[3] += part[lane * 33 + i + 3];
+      }
+      const float total = (nq[0] + nq[1]) + (nq[2] + nq[3]);
+      cf[2 * kMemChunk + lane] = q_scale / (fmaxf(fabsf(total * q_scale), expf(-m_mine)) + floor_);
     }
     __syncwarp();
   };
@@ -187,29 +226,44 @@ __global__ void matrix_memory_recurrence_kernel(const float* __restrict__ proj, 
       const float* cf = coef + (ch & 1) * 3 * kMemChunk;
       const int cnt = min(kMemChunk, n_tok - ch * kMemChunk);
       float* o_row = o_out + (size_t)(first + ch * kMemChunk) * H * dv + (size_t)h * dv + col;
-#pragma unroll 2
-      for (int tt = 0; tt < cnt; ++tt) {
-        const float keep = cf[tt];
-        const float wv = live ? cf[kMemChunk + tt] * v_s[tt * cols + col_local] : 0.f;
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      // a lane's share of S^T q for every token of the chunk; the shares cross the sixteen lanes once a chunk
+      float share[kMemChunk];
 #pragma unroll
-        for (int j = 0; j < DPL; j += 4) {
-          const float4 kk = *reinterpret_cast<const float4*>(k_s + tt * QS + j);
-          const float4 qq = *reinterpret_cast<const float4*>(q_s + tt * QS + j);
-          S[j] = fmaf(keep, S[j], wv * kk.x);
-          S[j + 1] = fmaf(keep, S[j + 1], wv * kk.y);
-          S[j + 2] = fmaf(keep, S[j + 2], wv * kk.z);
-          S[j + 3] = fmaf(keep, S[j + 3], wv * kk.w);
-          acc[0] = fmaf(S[j], qq.x, acc[0]);
-          acc[1] = fmaf(S[j + 1], qq.y, acc[1]);
-          acc[2] = fmaf(S[j + 2], qq.z, acc[2]);
-          acc[3] = fmaf(S[j + 3], qq.w, acc[3]);
+      for (int tt = 0; tt < kMemChunk; ++tt) {
+        share[tt] = 0.f;
+        if (tt < cnt) {
+          const float keep = cf[tt];
+          const float wv = cf[kMemChunk + tt] * v_s[tt * cols + col_local];      // (a column beyond dv: rubbish that is never written)
+          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int j = 0; j < DPL; j += 4) {
+            const float4 kk = *reinterpret_cast<const float4*>(k_s + tt * QS + j);
+            const float4 qq = *reinterpret_cast<const float4*>(q_s + tt * QS + j);
+            S[j] = fmaf(keep, S[j], wv * kk.x);
+            S[j + 1] = fmaf(keep, S[j + 1], wv * kk.y);
+            S[j + 2] = fmaf(keep, S[j + 2], wv * kk.z);
+            S[j + 3] = fmaf(keep, S[j + 3], wv * kk.w);
+            acc[0] = fmaf(S[j], qq.x, acc[0]);
+            acc[1] = fmaf(S[j + 1], qq.y, acc[1]);
+            acc[2] = fmaf(S[j + 2], qq.z, acc[2]);
+            acc[3] = fmaf(S[j + 3], qq.w, acc[3]);
+          }
+          share[tt] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
         }
-        float a = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-#pragma unroll
-        for (int o = 1; o < kMemLanes; o <<= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-        if (l == 0 && live) o_row[(size_t)tt * H * dv] = a * cf[2 * kMemChunk + tt];
       }
+      // halving exchanges: after the step with distance w a lane holds w sums, those of the tokens that share its bits
+      // above w; in the end lane l holds token l's
+#pragma unroll
+      for (int w = kMemChunk / 2; w >= 1; w >>= 1) {
+        const bool upper = (l & w) != 0;
+#pragma unroll
+        for (int i = 0; i < w; ++i) {
+          const float send = upper ? share[i] : share[i + w];
+          const float mine = upper ? share[i + w] : share[i];
+          share[i] = mine + __shfl_xor_sync(0xffffffffu, send, w);
+        }
+      }
+      if (live && l < cnt) o_row[(size_t)l * H * dv] = share[0] * cf[2 * kMemChunk + l];
     }
   }
   if (helper) {
@@ -272,11 +326,11 @@ extern "C" int srlm_matrix_memory_recurrence(const float* proj, long long ldp, c
   int cols = ((dv + tiles - 1) / tiles + 3) / 4 * 4;
   tiles = (dv + cols - 1) / cols;
   const int threads = cols * kMemLanes + 32;      // the walkers and the helper warp
-  if (threads > 1024) return refuse(ST_BAD_SIZE, "matrix_memory_recurrence: vdim=%d (at most 992)", dv);
+  if (threads > 1024) return refuse(ST_BAD_SIZE, "matrix_memory_recurrence: vdim=%d (at most 480)", dv);
   const int dpl_rows = (d + kMemLanes - 1) / kMemLanes;
-  const int dpl_t = dpl_rows <= 4 ? 4 : dpl_rows <= 8 ? 8 : dpl_rows <= 16 ? 16 : 32;
-  const size_t smem = ((size_t)3 * kMemChunk * (2 * kMemLanes * (dpl_t + 4) + cols + 2) + 2 * 3 * kMemChunk + kMemChunk * 33) *
-                      sizeof(float);
+  const int dpl_t = dpl_rows <= 4 ? 4 : dpl_rows <= 8 ? 8 : 16;
+  const int ls = dpl_t == 4 ? 4 : dpl_t + 4;
+  const size_t smem = ((size_t)3 * kMemChunk * (2 * kMemLanes * ls + cols + 2) + 2 * 3 * kMemChunk + kMemChunk * 33) * sizeof(float);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)tiles, (unsigned)H, (unsigned)n_entries);
   cfg.blockDim = dim3((unsigned)threads);
@@ -290,17 +344,17 @@ extern "C" int srlm_matrix_memory_recurrence(const float* proj, long long ldp, c
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   const int dpl = dpl_t;
+  const int vec = ldp % 4 == 0 && d % 4 == 0 && dv % 4 == 0 && ((uintptr_t)proj & 15) == 0;     // 16-byte copies into the chunks
 #define SRLM_MM(DPL)                                                                                                     \
   do {                                                                                                                   \
     auto kern = matrix_memory_recurrence_kernel<DPL>;                                                                    \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
     cudaLaunchKernelEx(&cfg, kern, proj, ldp, bias_i, bias_f, cap, floor_, state, state_stride, cu_q, slots, o_out, H, d, \
-                       dv, cols);                                                                                        \
+                       dv, cols, vec);                                                                                   \
   } while (0)
   if (dpl <= 4) SRLM_MM(4);
   else if (dpl <= 8) SRLM_MM(8);
-  else if (dpl <= 16) SRLM_MM(16);
-  else SRLM_MM(32);
+  else SRLM_MM(16);
 #undef SRLM_MM
   return launched();
 }

@@ -771,7 +771,7 @@ def test_ramped_rotary_table_and_norm_of_columns():
     from safetyraise_lmengine_b200.parts import ModelContext
     from safetyraise_lmengine_b200.parts.position import RotaryHalf
     dev = torch.device("cuda:0")
-    for rot in (rot_of(16, 50000.0, (8.0, 1024, 32.0, 1.0)), rot_of(6, 100.0, (3.0, 30, 2.0, 0.25)), rot_of(8, 10000.0, None)):
+    for rot in (rot_of(12, 30000.0, (6.0, 512, 16.0, 2.0)), rot_of(6, 100.0, (3.0, 30, 2.0, 0.25)), rot_of(8, 10000.0, None)):
         sc = rot.get("scaling")
         spec = PositionSpec("rotary_half", theta=rot["base"], rotary_dim=rot["dims"], head_dim=rot["dims"],
                             ramp=(sc["factor"], sc["original"], sc["fast"], sc["slow"]) if sc else None)

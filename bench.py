@@ -618,7 +618,7 @@ def dovorax_config(size: dict, kinds) -> dict:
     layer's feed-forward dense (three widths), the others' 16 ungated experts of three quarters of a width in 4 groups
     of which 2 are kept, 4 a token, plus a shared one of one width and a half."""
     W, H, G = size["width"], size["heads"], size["kv_heads"]
-    scaling = {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+    scaling = {"factor": 16.0, "original": 4096, "fast": 24.0, "slow": 2.0}
     mixers = {
         "latent_attention": {"heads": H, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 3 * W // 4,
                              "scale": 192 ** -0.5, "mask": {"size": DOVORAX_WINDOW},

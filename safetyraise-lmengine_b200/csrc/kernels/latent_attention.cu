@@ -29,12 +29,15 @@ __device__ __forceinline__ float rotated_element(const TP* __restrict__ src, int
 
 constexpr int kTokTile = 16;
 
-// One block per token.  proj row: [.. | c_raw (rank) | kr_raw (rot) | ..] starting at column c_off.
-template <typename TP, typename TC>
+// One block per token.  proj row: [.. | c_raw (rank) | kr_raw (rot) | ..] starting at column c_off.  q_out != null: the
+// same block also norms the q_width columns from q_col (a latent of the queries in the same stacked projection) with
+// q_norm_w into q_out [T, q_width].
+template <typename TP, typename TC, typename TQ>
 __global__ void latent_append_kernel(const TP* __restrict__ proj, long long ldp, int c_off,
                                      const float* __restrict__ norm_w, float eps, const float* __restrict__ cos_t,
                                      const float* __restrict__ sin_t, int pairs, int halves, TC* __restrict__ cache,
-                                     const int* __restrict__ kv_slot, int rank, int rot) {
+                                     const int* __restrict__ kv_slot, int rank, int rot, int q_col, int q_width,
+                                     const float* __restrict__ q_norm_w, TQ* __restrict__ q_out) {
   pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
   pdl_trigger();
   __shared__ float scratch[32];
@@ -51,6 +54,17 @@ __global__ void latent_append_kernel(const TP* __restrict__ proj, long long ldp,
   for (int i = threadIdx.x; i < rot; i += blockDim.x) {
     const float v = i < 2 * pairs ? rotated_element(p + rank, i, (size_t)t, pairs, halves, cos_t, sin_t) : to_float(p[rank + i]);
     row[rank + i] = from_float<TC>(v);
+  }
+  if (q_out) {
+    const TP* q = proj + (size_t)t * ldp + q_col;
+    float qs = 0.f;
+    for (int i = threadIdx.x; i < q_width; i += blockDim.x) {
+      const float v = to_float(q[i]);
+      qs += v * v;
+    }
+    const float q_inv = 1.0f / sqrtf(block_sum(qs, scratch) / (float)q_width + eps);
+    for (int i = threadIdx.x; i < q_width; i += blockDim.x)
+      q_out[(size_t)t * q_width + i] = from_float<TQ>(to_float(q[i]) * q_inv * q_norm_w[i]);
   }
 }
 
@@ -249,13 +263,20 @@ using namespace srlm;
 
 extern "C" int srlm_latent_append(const void* proj, int proj_dtype, long long ldp, int c_off, const float* norm_w,
                                   float eps, const float* cos_t, const float* sin_t, int pairs, int halves, void* cache,
-                                  int cache_dtype, const int* kv_slot, int T, int rank, int rot, cudaStream_t stream) {
+                                  int cache_dtype, const int* kv_slot, int T, int rank, int rot, int q_col, int q_width,
+                                  const float* q_norm_w, void* q_out, int q_dtype, cudaStream_t stream) {
   if (T <= 0) return ST_OK;
   if (rank <= 0 || rot < 0 || 2 * pairs > rot || c_off < 0 || ldp < c_off + rank + rot || !(eps > 0.f) ||
-      (pairs > 0 && (!cos_t || !sin_t)))
+      (pairs > 0 && (!cos_t || !sin_t)) || (q_out && (q_width <= 0 || q_col < 0 || ldp < q_col + q_width || !q_norm_w)))
     return refuse(ST_BAD_SIZE, "latent_append: rank=%d rot=%d pairs=%d c_off=%d ldp=%lld", rank, rot, pairs, c_off, ldp);
-  SRLM_LATENT_TYPES(proj_dtype, cache_dtype, (launch_pdl(latent_append_kernel<TP, TW>, dim3(T), dim3(128), 0, stream, 
-      (const TP*)proj, ldp, c_off, norm_w, eps, cos_t, sin_t, pairs, halves, (TW*)cache, kv_slot, rank, rot)));
+#define SRLM_APPEND(TQ)                                                                                              \
+  SRLM_LATENT_TYPES(proj_dtype, cache_dtype, (launch_pdl(latent_append_kernel<TP, TW, TQ>, dim3(T), dim3(128), 0, stream, \
+      (const TP*)proj, ldp, c_off, norm_w, eps, cos_t, sin_t, pairs, halves, (TW*)cache, kv_slot, rank, rot, q_col,  \
+      q_width, q_norm_w, (TQ*)q_out)))
+  if (!q_out || q_dtype == DT_F32) SRLM_APPEND(float);
+  else if (q_dtype == DT_BF16) SRLM_APPEND(bf16);
+  else return refuse(ST_BAD_DTYPE, "latent_append: the normed queries' dtype %d", q_dtype);
+#undef SRLM_APPEND
   return launched();
 }
 

@@ -1,6 +1,7 @@
 // Kernels of blocks that norm after the sum, and small elementwise companions:
 //
-//   postnorm_scale_add   x <- w' * (alpha x + delta) / sqrt(mean((alpha x + delta)^2) + eps), w' = w or 1 + w; the float32
+//   postnorm_scale_add   x <- w' * (alpha x + delta) / sqrt(mean((alpha x + delta)^2) + eps), w' = w or 1 + w (delta one tensor,
+//                        or w1 d1 + w2 d2 for two results that are summed with weights on their way in); the float32
 //                        stream is rewritten in place and, optionally, copied in the activation dtype for the next
 //                        sublayer's products (one kernel, one pass over the row, which stays in shared memory)
 //   rmsnorm_columns      RMS norm of a range of columns of a float32 row-major tensor (a latent inside a stacked projection)
@@ -19,6 +20,7 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 
 template <typename TD, typename TO>
 __global__ void postnorm_scale_add_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+                                          const TD* __restrict__ delta2, float w1, float w2,
                                           const float* __restrict__ weight, float alpha, float eps, int unit_offset,
                                           TO* __restrict__ out, int H) {
   pdl_wait();
@@ -28,7 +30,9 @@ __global__ void postnorm_scale_add_kernel(float* __restrict__ residual, const TD
   const size_t base = (size_t)blockIdx.x * H;
   float ss = 0.f;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float v = fmaf(alpha, residual[base + i], delta ? to_float(delta[base + i]) : 0.f);
+    float add = delta ? to_float(delta[base + i]) : 0.f;
+    if (delta2) add = fmaf(w2, to_float(delta2[base + i]), w1 * add);
+    const float v = fmaf(alpha, residual[base + i], add);
     row[i] = v;
     ss += v * v;
   }
@@ -90,20 +94,22 @@ using namespace srlm;
     else return refuse(ST_BAD_DTYPE, "dtype codes %d, %d are not known", (int)(da), (int)(db));        \
   } while (0)
 
-// residual float32 [T, H] in place; delta [T, H] (delta_dtype) or null; out [T, H] (out_dtype) or null
-extern "C" int srlm_postnorm_scale_add(float* residual, const void* delta, int delta_dtype, const float* weight,
-                                       float alpha, float eps, int unit_offset, void* out, int out_dtype, int T, int H,
-                                       cudaStream_t stream) {
+// residual float32 [T, H] in place; delta [T, H] (delta_dtype) or null; delta2 [T, H] (delta_dtype) or null: then the addend
+// is w1 delta + w2 delta2; out [T, H] (out_dtype) or null
+extern "C" int srlm_postnorm_scale_add(float* residual, const void* delta, const void* delta2, float w1, float w2,
+                                       int delta_dtype, const float* weight, float alpha, float eps, int unit_offset,
+                                       void* out, int out_dtype, int T, int H, cudaStream_t stream) {
   if (T <= 0) return ST_OK;
   const size_t smem = (size_t)H * sizeof(float);
-  if (H <= 0 || smem > 160 * 1024 || !(eps > 0.f)) return refuse(ST_BAD_SIZE, "postnorm_scale_add: H=%d eps=%g", H, eps);
+  if (H <= 0 || smem > 160 * 1024 || !(eps > 0.f) || (delta2 && !delta))
+    return refuse(ST_BAD_SIZE, "postnorm_scale_add: H=%d eps=%g", H, eps);
   const int threads = H >= 2048 ? 512 : 256;
 #define SRLM_POSTNORM(TD, TO)                                                                                    \
   do {                                                                                                           \
     auto kern = postnorm_scale_add_kernel<TD, TO>;                                                               \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    launch_pdl(kern, dim3(T), dim3(threads), smem, stream, residual, (const TD*)delta, weight, alpha, eps,       \
-               unit_offset, (TO*)out, H);                                                                        \
+    launch_pdl(kern, dim3(T), dim3(threads), smem, stream, residual, (const TD*)delta, (const TD*)delta2, w1, w2, \
+               weight, alpha, eps, unit_offset, (TO*)out, H);                                                    \
   } while (0)
   SRLM_TWO_TYPES(delta ? delta_dtype : DT_F32, out ? out_dtype : DT_F32, TD, TO, SRLM_POSTNORM(TD, TO));
 #undef SRLM_POSTNORM

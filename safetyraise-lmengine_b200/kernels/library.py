@@ -1098,16 +1098,22 @@ class KernelLibrary:
                                                       _stream()), "paired_rmsnorm_mean")
 
     # ---- blocks that norm after the sum, and their elementwise companions ---------------------------
-    def postnorm_scale_add(self, residual, delta, weight, alpha, eps, unit_offset=False, out=None):
+    def postnorm_scale_add(self, residual, delta, weight, alpha, eps, unit_offset=False, out=None, terms=None):
         """residual <- w' * y / sqrt(mean(y^2) + eps) with y = alpha * residual + delta and w' = weight (or 1 + weight),
         in place (float32 [T, H]); delta [T, H] in float32 or the activation dtype, or None; ``out``: a copy of the
-        new rows in its own dtype."""
+        new rows in its own dtype.  terms ((d1, w1), (d2, w2)) in place of delta: the addend is w1 d1 + w2 d2."""
         T, H = residual.shape
+        delta2, w1, w2 = None, 1.0, 0.0
+        if terms is not None:
+            (delta, w1), (delta2, w2) = terms
+            if delta2.dtype != delta.dtype or delta2.shape != delta.shape:
+                raise ShapeError("postnorm_scale_add: two addends of one shape and dtype")
         if residual.dtype != torch.float32 or (delta is not None and tuple(delta.shape) != (T, H)) or \
                 (out is not None and tuple(out.shape) != (T, H)):
             raise ShapeError(f"postnorm_scale_add: residual {tuple(residual.shape)} {residual.dtype}")
         self._check(self.lib.srlm_postnorm_scale_add(
-            _ptr(residual), _ptr(delta), dtype_code(delta.dtype) if delta is not None else 0, _ptr(weight), C.c_float(alpha),
+            _ptr(residual), _ptr(delta), _ptr(delta2), C.c_float(w1), C.c_float(w2),
+            dtype_code(delta.dtype) if delta is not None else 0, _ptr(weight), C.c_float(alpha),
             C.c_float(eps), C.c_int(int(unit_offset)), _ptr(out), dtype_code(out.dtype) if out is not None else 0,
             C.c_int(T), C.c_int(H), _stream()), "postnorm_scale_add")
 
@@ -1214,15 +1220,18 @@ class KernelLibrary:
                                                     C.c_int(int(in_segments)), _stream()), "linear_recurrence")
 
     # ---- attention over a cached latent ----------------------------------------------------
-    def latent_append(self, proj, c_off, norm_w, eps, rotation, cache, kv_slot, rank, rot):
-        """cache row of each token = [rms_norm(proj[c_off : c_off + rank]) * norm_w | rotated proj[.. + rot]]."""
+    def latent_append(self, proj, c_off, norm_w, eps, rotation, cache, kv_slot, rank, rot, q_norm=None):
+        """cache row of each token = [rms_norm(proj[c_off : c_off + rank]) * norm_w | rotated proj[.. + rot]].
+        q_norm (column, width, weight, out): the same kernel also writes out [T, width] = rms_norm(proj[column : column +
+        width]) * weight (a latent of the queries that the same stacked projection holds)."""
         pairs = rotation.pairs if rotation is not None else 0
+        q_col, q_width, q_w, q_out = q_norm if q_norm is not None else (0, 0, None, None)
         self._check(self.lib.srlm_latent_append(
             _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), C.c_int(c_off), _ptr(norm_w),
             C.c_float(eps), _ptr(rotation.cos if pairs else None), _ptr(rotation.sin if pairs else None),
             C.c_int(pairs), C.c_int(int(bool(pairs and not rotation.interleaved))), _ptr(cache), dtype_code(cache.dtype),
-            _ptr(kv_slot), C.c_int(proj.shape[0]),
-            C.c_int(rank), C.c_int(rot), _stream()), "latent_append")
+            _ptr(kv_slot), C.c_int(proj.shape[0]), C.c_int(rank), C.c_int(rot), C.c_int(q_col), C.c_int(q_width),
+            _ptr(q_w), _ptr(q_out), dtype_code(q_out.dtype) if q_out is not None else 0, _stream()), "latent_append")
 
     def latent_absorb(self, proj, uk, rotation, q_out, heads, dim, rot, rank):
         """q_out float32 [T, heads, rank + rot] = per head [uk_h^T q_h | rotated rest of the head]; uk [heads, dim, rank]."""

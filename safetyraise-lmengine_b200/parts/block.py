@@ -241,7 +241,10 @@ class PostNormBlock(Block):
         return PreNormBlock.tensor_decls(spec, prefix)       # the same parts under the same names
 
     def _join(self, residual, sub, norm, copy):
-        ops.postnorm_scale_add(residual, sub, norm.weight, self.alpha, norm.spec.eps, norm.spec.unit_offset, copy)
+        """sub: a sublayer's result, or two results with their weights ((y1, w1), (y2, w2)) that this kernel sums."""
+        terms = sub if isinstance(sub, tuple) else None
+        ops.postnorm_scale_add(residual, None if terms else sub, norm.weight, self.alpha, norm.spec.eps,
+                               norm.spec.unit_offset, copy, terms=terms)
 
     def forward(self, ctx, residual, pending, run_step: RunStep, next_block=None):
         T = residual.shape[0]
@@ -256,7 +259,10 @@ class PostNormBlock(Block):
                 ops.residual_add(residual, pending)
             if low:
                 ops.cast(residual, x)
-        mixed = self.mixer.forward(ctx, x, run_step)
+        if getattr(self.mixer, "offers_terms", False):      # a weighted pair: its sum rides in the kernel below
+            mixed = self.mixer.forward(ctx, x, run_step, as_terms=True)
+        else:
+            mixed = self.mixer.forward(ctx, x, run_step)
         self._join(residual, mixed, self.mixer_norm, x if low else None)
         if self.feed_forward is not None:
             self._join(residual, self.feed_forward.forward(ctx, x), self.ff_norm, x if low else None)

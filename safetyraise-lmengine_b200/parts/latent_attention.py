@@ -106,13 +106,14 @@ class LatentAttention(Part):
         proj = self.proj(ctx, x, "latent.proj", out_dtype=torch.float32)
         cache, _, group = ctx.cache.kv_of_entry(run_step.cache)
         rot = self.position.rotation(ctx) if self.position is not None else None
-        if s.own_kv:
+        cq = ctx.workspace.get("latent.cq", T, s.q_rank, ctx.dtype) if s.q_rank else None
+        if s.own_kv:       # the kernel that norms and appends the latent norms the queries' latent too
             ops.latent_append(proj, self.c_off, self.latent_norm_w, s.latent_norm_eps, rot, cache, ctx.kv_slot[group],
-                              s.kv_rank, s.rot_dim)
+                              s.kv_rank, s.rot_dim, q_norm=(0, s.q_rank, self.q_norm_w, cq) if s.q_rank else None)
+        elif s.q_rank:
+            ops.rmsnorm_columns(proj, 0, s.q_rank, self.q_norm_w, s.latent_norm_eps, cq)
         q_heads = proj                 # heads x [dim | rot_dim] lead the row
         if s.q_rank:
-            cq = ctx.workspace.get("latent.cq", T, s.q_rank, ctx.dtype)
-            ops.rmsnorm_columns(proj, 0, s.q_rank, self.q_norm_w, s.latent_norm_eps, cq)
             q_heads = self.q_up(ctx, cq, "latent.q_heads_raw", out_dtype=torch.float32)
         gated = ctx.workspace.get("latent.out", T, s.heads * s.v_head_dim, ctx.dtype)
         if (self.up_kv is not None and ctx.max_q_len > 4

@@ -69,10 +69,18 @@ class SideBySide(Part):
                                                                    more_caches=entries[at + 1:at + self.entries_of[k]])
         return got
 
-    def forward(self, ctx, x: torch.Tensor, run_step: RunStep) -> torch.Tensor:
-        # the mixers' results in float32: they are normed before anything rounds them
+    @property
+    def offers_terms(self) -> bool:
+        """Whether forward(..., as_terms=True) hands back the mixers' results with their weights instead of their sum
+        (for a block whose own kernel adds them to the stream)."""
+        return self.spec.combine == "weighted_sum"
+
+    def forward(self, ctx, x: torch.Tensor, run_step: RunStep, as_terms: bool = False):
+        # the mixers' results in float32: they are normed, or summed, before anything rounds them
         ys = [m.forward(ctx, x, self._step_of(run_step, k), out_dtype=torch.float32) for k, m in enumerate(self.mixers)]
         out = ctx.workspace.get("side.out", x.shape[0], self.spec.hidden_size, ctx.dtype)
+        if self.spec.combine == "weighted_sum" and as_terms:
+            return tuple(zip(ys, self.spec.weights))
         if self.spec.combine == "weighted_sum":
             ops.weighted_sum(ys[0], self.spec.weights[0], ys[1], self.spec.weights[1], out)
             return out

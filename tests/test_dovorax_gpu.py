@@ -763,6 +763,12 @@ def test_norm_behind_the_scaled_sum(H, delta_dtype, out_dtype):
     assert (res.cpu() - ref).abs().max() <= 1e-5 * ref.abs().max()
     if out is not None:
         assert torch.equal(out.cpu(), res.cpu().to(out_dtype))
+    # two results summed with weights on their way in
+    d2 = torch.randn(T, H, generator=g).to(delta_dtype)
+    ref = P.rms_norm(1.7 * x.double() + 0.8 * d.double() - 0.5 * d2.double(), w, 1e-5, one_plus=True)
+    res = x.to(dev)
+    ops.postnorm_scale_add(res, None, w.to(dev), 1.7, 1e-5, True, out, terms=((d.to(dev), 0.8), (d2.to(dev), -0.5)))
+    assert (res.cpu() - ref).abs().max() <= 1e-5 * ref.abs().max()
 
 
 def test_ramped_rotary_table_and_norm_of_columns():

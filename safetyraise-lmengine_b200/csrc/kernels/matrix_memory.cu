@@ -6,7 +6,8 @@
 //
 // in float32, token by token.  The stacked projection row holds  q (H d) | k (H d) | v (H dv) | output gate (H dv) |
 // i (H) | f (H), float32; i <- cap tanh((i + b_i) / cap), f <- log logistic(cap tanh((f + b_f) / cap)); q is scaled by
-// 1 / sqrt(d).  A request's state row: S [H][d][dv] | n [H][d] | m [H], zeros for a new request.
+// 1 / sqrt(d).  A request's state row: S [H][dv][d] (a column of S, the d rows of one value element, is contiguous: a
+// walking lane's rows are neighbours in memory) | n [H][d] | m [H], zeros for a new request.
 //
 // matrix_memory_recurrence: a block takes one entry, one head and a tile of the value columns; the tiles of a head are a
 // thread-block cluster.  Its walking warps hold S: sixteen lanes share a column, a lane DPL neighbouring rows of it in
@@ -44,7 +45,7 @@ __global__ void matrix_memory_recurrence_kernel(const float* __restrict__ proj, 
                                                 const float* __restrict__ bias_f, float cap, float floor_,
                                                 float* __restrict__ state, long long state_stride,
                                                 const int* __restrict__ cu_q, const int* __restrict__ slots,
-                                                float* __restrict__ o_out, int H, int d, int dv, int cols, int vec) {
+                                                float* __restrict__ o_out, int H, int d, int dv, int cols, int vec, int nbuf) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ __align__(16) float mm_smem[];
@@ -54,7 +55,7 @@ __global__ void matrix_memory_recurrence_kernel(const float* __restrict__ proj, 
   // raw chunks, three buffers of: q [chunk][QS] | k [chunk][QS] | v [chunk][cols] | gate logits [chunk][2];
   // then two buffers of what the helper makes of a chunk: keep | write | 1 / denominator [chunk] each; then its scratch
   const int per_raw = kMemChunk * (2 * QS + cols + 2);
-  float* coef = mm_smem + 3 * per_raw;
+  float* coef = mm_smem + nbuf * per_raw;           // nbuf: 3, or 1 when no entry of the step has more than one chunk
   float* part = coef + 2 * 3 * kMemChunk;          // [chunk][33]: the helper lanes' shares of n . q
   const int e = blockIdx.z, h = blockIdx.y, c0 = blockIdx.x * cols;
   const int first = cu_q[e], n_tok = cu_q[e + 1] - first;
@@ -75,7 +76,7 @@ __global__ void matrix_memory_recurrence_kernel(const float* __restrict__ proj, 
 
   auto fetch = [&](int chunk) {
     if (chunk < chunks) {
-      float* base = mm_smem + (chunk % 3) * per_raw;
+      float* base = mm_smem + (chunk % nbuf) * per_raw;
       const int t0 = chunk * kMemChunk, cnt = min(kMemChunk, n_tok - t0);
       if (vec) {        // 16-byte copies: four neighbouring rows of q and of k, four neighbouring columns of v
         constexpr int RP4 = kMemLanes * DPL / 4;
@@ -135,7 +136,7 @@ __global__ void matrix_memory_recurrence_kernel(const float* __restrict__ proj, 
 #pragma unroll
     for (int j = 0; j < DPL; ++j) {
       const int r = l * DPL + j;
-      S[j] = (live && r < d) ? S_g[(size_t)r * dv + col] : 0.f;
+      S[j] = (live && r < d) ? S_g[(size_t)col * d + r] : 0.f;
     }
   }
   fetch(0);
@@ -145,7 +146,7 @@ __global__ void matrix_memory_recurrence_kernel(const float* __restrict__ proj, 
 
   // what the helper makes of chunk ch (its raw data has landed and is visible): keep, write, 1 / denominator per token
   auto prepare = [&](int ch) {
-    float* base = mm_smem + (ch % 3) * per_raw;
+    float* base = mm_smem + (ch % nbuf) * per_raw;
     const float* q_s = base;
     const float* k_s = base + kMemChunk * QS;
     float* g_s = base + kMemChunk * (2 * QS + cols);
@@ -219,7 +220,7 @@ __global__ void matrix_memory_recurrence_kernel(const float* __restrict__ proj, 
     if (helper) {
       if (ch + 1 < chunks) prepare(ch + 1);
     } else {
-      const float* base = mm_smem + (ch % 3) * per_raw;
+      const float* base = mm_smem + (ch % nbuf) * per_raw;
       const float* q_s = base + l * LS;
       const float* k_s = base + kMemChunk * QS + l * LS;
       const float* v_s = base + 2 * kMemChunk * QS;
@@ -279,7 +280,7 @@ __global__ void matrix_memory_recurrence_kernel(const float* __restrict__ proj, 
 #pragma unroll
     for (int j = 0; j < DPL; ++j) {
       const int r = l * DPL + j;
-      if (r < d) S_g[(size_t)r * dv + col] = S[j];
+      if (r < d) S_g[(size_t)col * d + r] = S[j];
     }
   }
 }
@@ -314,8 +315,8 @@ extern "C" int srlm_matrix_memory_state_size(int H, int d, int dv) { return H * 
 // proj float32 [T, ldp] as laid out above; state float32 [slots, state_stride]; o_out float32 [T, H dv]
 extern "C" int srlm_matrix_memory_recurrence(const float* proj, long long ldp, const float* bias_i, const float* bias_f,
                                              float cap, float floor_, float* state, long long state_stride,
-                                             const int* cu_q, const int* slots, float* o_out, int n_entries, int H, int d,
-                                             int dv, cudaStream_t stream) {
+                                             const int* cu_q, const int* slots, float* o_out, int n_entries, int max_q_len,
+                                             int H, int d, int dv, cudaStream_t stream) {
   if (n_entries <= 0) return ST_OK;
   if (H <= 0 || d <= 0 || dv <= 0 || d > 256 || !(cap > 0.f) || ldp < 2LL * H * d + 2LL * H * dv + 2 * H ||
       state_stride < (long long)H * d * dv + (long long)H * d + H || n_entries > 65535 || H > 65535)
@@ -330,7 +331,9 @@ extern "C" int srlm_matrix_memory_recurrence(const float* proj, long long ldp, c
   const int dpl_rows = (d + kMemLanes - 1) / kMemLanes;
   const int dpl_t = dpl_rows <= 4 ? 4 : dpl_rows <= 8 ? 8 : 16;
   const int ls = dpl_t == 4 ? 4 : dpl_t + 4;
-  const size_t smem = ((size_t)3 * kMemChunk * (2 * kMemLanes * ls + cols + 2) + 2 * 3 * kMemChunk + kMemChunk * 33) * sizeof(float);
+  // steps whose entries all fit one chunk (decode steps) need one buffer of raw tokens, and more blocks fit an SM
+  const int nbuf = max_q_len > 0 && max_q_len <= kMemChunk ? 1 : 3;
+  const size_t smem = ((size_t)nbuf * kMemChunk * (2 * kMemLanes * ls + cols + 2) + 2 * 3 * kMemChunk + kMemChunk * 33) * sizeof(float);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)tiles, (unsigned)H, (unsigned)n_entries);
   cfg.blockDim = dim3((unsigned)threads);
@@ -350,7 +353,7 @@ extern "C" int srlm_matrix_memory_recurrence(const float* proj, long long ldp, c
     auto kern = matrix_memory_recurrence_kernel<DPL>;                                                                    \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
     cudaLaunchKernelEx(&cfg, kern, proj, ldp, bias_i, bias_f, cap, floor_, state, state_stride, cu_q, slots, o_out, H, d, \
-                       dv, cols, vec);                                                                                   \
+                       dv, cols, vec, nbuf);                                                                             \
   } while (0)
   if (dpl <= 4) SRLM_MM(4);
   else if (dpl <= 8) SRLM_MM(8);

@@ -1186,11 +1186,13 @@ class KernelLibrary:
     # ---- the matrix memory ----------------------------------------------------------------------------
     def matrix_memory_recurrence(self, ctx, proj, bias_i, bias_f, cap, floor, state, o_out, H, d, dv):
         """o_out float32 [T, H dv]: the read-outs of a matrix memory with exponential gates, token by token, from the
-        stacked projection q | k | v | output gate | i | f (float32); state float32 [slots, H d dv + H d + H]."""
+        stacked projection q | k | v | output gate | i | f (float32); state float32 [slots, H dv d + H d + H]
+        (S of a head with the rows of a value column contiguous, then n, then m)."""
         self._check(self.lib.srlm_matrix_memory_recurrence(
             _ptr(proj), C.c_longlong(proj.stride(0)), _ptr(bias_i), _ptr(bias_f), C.c_float(cap), C.c_float(floor),
             _ptr(state), C.c_longlong(state.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.slots), _ptr(o_out),
-            C.c_int(ctx.n_entries), C.c_int(H), C.c_int(d), C.c_int(dv), _stream()), "matrix_memory_recurrence")
+            C.c_int(ctx.n_entries), C.c_int(ctx.max_q_len), C.c_int(H), C.c_int(d), C.c_int(dv), _stream()),
+            "matrix_memory_recurrence")
 
     def matrix_memory_output(self, o, norm_w, eps, proj, g_off, out, H, dv):
         """out [T, H dv] = per head o / sqrt(mean(o^2) + eps), times norm_w (float32 [H dv]), times the logistic of the

@@ -649,7 +649,7 @@ def test_matrix_memory_carried_through_steps_and_slots(H, d, dv, cap):
         # are the worst conditioned ones
         assert (torch.cat(got[s]) - ref).abs().max() <= 2e-4 * ref.abs().max(), s
         row = state[s].cpu().double()
-        assert (row[:H * d * dv].reshape(H, d, dv) - S).abs().max() <= 2e-5 * max(S.abs().max(), 1e-30)
+        assert (row[:H * d * dv].reshape(H, dv, d).transpose(1, 2) - S).abs().max() <= 2e-5 * max(S.abs().max(), 1e-30)
         assert (row[H * d * dv:H * d * dv + H * d].reshape(H, d) - n).abs().max() <= 2e-5 * max(n.abs().max(), 1e-30)
         assert (row[-H:] - m).abs().max() <= 1e-5 * max(m.abs().max(), 1.0)
     assert state[0].abs().max() == 0 and state[2].abs().max() == 0

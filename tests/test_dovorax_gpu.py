@@ -844,6 +844,77 @@ def test_attention_with_one_more_term_and_a_far_key(heads, kv_heads, dk, dv, win
         assert (out.float().cpu() - ref[first:]).abs().max() <= tol * ref.abs().max(), first
 
 
+@pytest.mark.parametrize("window", [45, 0])
+def test_latent_attention_on_both_roads_at_a_window_edge(window):
+    """Pages of [latent | key part] for 200 keys; the last query's weight sits on a key just inside its window (far back
+    without one), the same key part just outside it belongs to a latent whose values would show; the pages wholly behind
+    the step's reach are gone.  In the latent space (decode steps, float32) and in the heads' own space (bfloat16 prompts),
+    whole, as a portion and as one token, against the plain per-head attention."""
+    from safetyraise_lmengine_b200.kernels import ops
+    dev, page, L = "cuda:0", 16, 200
+    H, dim, rot, dv, rank = 4, 32, 16, 64, 64
+    g = torch.Generator().manual_seed(7 + window)
+    bf = lambda t: t.bfloat16().float()
+    c, kr = bf(torch.randn(L, rank, generator=g)), bf(torch.randn(L, rot, generator=g))
+    uk, uv = bf(0.2 * torch.randn(H * dim, rank, generator=g)), bf(0.2 * torch.randn(H * dv, rank, generator=g))
+    q = torch.randn(L, H, dim + rot, generator=g)
+    scale = 0.7 * (dim + rot) ** -0.5
+    far = L - window if window else 5
+    kr[far] *= 3.0
+    q[L - 1, :, :dim] = 0.0
+    q[L - 1, :, dim:] = 14.0 * kr[far] / ((kr[far] ** 2).sum() * scale)
+    if window:
+        kr[L - 1 - window], c[L - 1 - window] = kr[far], 6.0
+    kn = (c.double() @ uk.double().T).view(L, H, dim)
+    v = (c.double() @ uv.double().T).view(L, H, dv)
+    s_ = (torch.einsum("ihd,jhd->hij", q[..., :dim].double(), kn) + torch.einsum("ihd,jd->hij", q[..., dim:].double(), kr.double())) * scale
+    a = P.softmax_rows(s_, P.visible(L, window or None))
+    ref = torch.einsum("hij,jhd->ihd", a, v).reshape(L, H * dv)
+    assert a[:, L - 1, far].min() > 0.5
+    n_pages = (L + page - 1) // page
+    order = torch.randperm(n_pages, generator=g).tolist()
+    uk_d = uk.to(dev).bfloat16()
+    uv_d = uv.to(dev).bfloat16()
+    up_kv = torch.cat([uk_d, uv_d]).contiguous()
+    for dtype in (torch.float32, torch.bfloat16):
+        cache = torch.zeros(n_pages, 1, page, rank + rot, device=dev, dtype=dtype)
+        for t in range(L):
+            cache[order[t // page], 0, t % page] = torch.cat([c[t], kr[t]]).to(dev)
+        for first in (0, L - 60, L - 1):
+            n = L - first
+            reach = max(0, first - window + 1) if window else 0          # the first key any row of the step sees
+            table = torch.tensor([[-1 if (pg + 1) * page <= reach else order[pg] for pg in range(n_pages)]],
+                                 dtype=torch.int32, device=dev)
+            ctx = _Ctx([n], [L], dev)
+            ctx.max_kv_len = L
+            qd = q[first:].reshape(n, -1).to(dev).contiguous()
+            tol = 2e-5 if dtype == torch.float32 else 2e-2
+            # in the latent space
+            w_k = (uk_d if dtype == torch.bfloat16 else uk.to(dev)).view(H, dim, rank).contiguous()
+            w_v = (uv_d if dtype == torch.bfloat16 else uv.to(dev)).view(H, dv, rank).transpose(1, 2).contiguous()
+            q_lat = torch.empty(n, H * (rank + rot), device=dev)
+            ops.latent_absorb(qd, w_k, None, q_lat, H, dim, rot, rank)
+            o_lat = torch.empty(n, H * rank, device=dev)
+            ops.paged_attention_general(ctx, q_lat, cache, None, o_lat, table, None, H, 1, rank + rot, rank, scale, window)
+            out = torch.empty(n, H * dv, device=dev, dtype=dtype)
+            ops.latent_expand(o_lat, w_v, qd, -1, out, H, rank, dv)
+            assert (out.float().cpu() - ref[first:]).abs().max() <= tol * ref.abs().max(), (dtype, first, "latent space")
+            if dtype != torch.bfloat16 or n <= 4:
+                continue
+            # in the heads' own space: the latents from the step's reach on, one product for all heads' keys and values
+            cu_kv = torch.tensor([-reach], dtype=torch.int32, device=dev)
+            kv_first = torch.tensor([reach], dtype=torch.int32, device=dev)
+            latents = torch.zeros(L - reach, rank, device=dev, dtype=dtype)
+            ops.latent_gather(ctx, cache, latents, table, cu_kv, rank, kv_first)
+            kv_rows = torch.empty(L - reach, H * (dim + dv), device=dev, dtype=dtype)
+            ops.gemm(latents, up_kv, kv_rows)
+            qh = torch.empty(n, H * (dim + rot), device=dev)
+            ops.latent_rotate_q(qd, None, qh, H, dim, rot)
+            out = torch.empty(n, H * dv, device=dev, dtype=dtype)
+            ops.latent_prefill_attention(ctx, qh, cache, kv_rows, cu_kv, out, table, H, dim, rot, dv, rank, H * dim, scale, window)
+            assert (out.float().cpu() - ref[first:]).abs().max() <= tol * ref.abs().max(), (dtype, first, "head space")
+
+
 def _experts_plain(x, up, down, choice, weight, shared):
     out = torch.zeros(x.shape[0], down.shape[1], dtype=torch.float64)
     for t in range(x.shape[0]):
